@@ -58,6 +58,8 @@ def _args():
                     help="2: ping-pong schedule over two nano-batches per rank")
     ap.add_argument("--no-fuse-qkv-rope", action="store_true",
                     help="separate RoPE / dispatch kernel instead of the QKV GEMM epilogue (for A/B timing)")
+    ap.add_argument("--phase-timers", action="store_true",
+                    help="CUDA-event phase timers in the device-timed region; the JSON line gains phases_ms_per_step")
     ap.add_argument("--recompute", default="keep_attn", choices=["full", "keep_attn"],
                     help="keep_attn: recompute every layer in backward except core attention, whose output is kept "
                          "(HBM or pinned host memory); falls back to full when neither has room")
@@ -187,7 +189,7 @@ def main() -> None:
             staged.append((hb, trainer.to_device(hb)))
     barrier()
     from distca_b200.utils import timers
-    timers.enable(trainer.cad is not None)   # CUDA-event phase timers (no host sync) for the CAD metrics
+    timers.enable(trainer.cad is not None or a.phase_timers)   # CUDA-event phase timers (no host sync)
     launches0 = _lib.LAUNCHES
     e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
     e0.record()
@@ -264,6 +266,8 @@ def main() -> None:
             "loss_first_last": [losses[0], losses[-1]],
             "impl": "ours",
         }
+        if a.phase_timers:
+            out["phases_ms_per_step"] = {k: round(v / a.steps, 2) for k, v in sorted(phases.items())}
         if trainer.cad is not None:
             out["cad"] = {"planned_imbalance_after": trainer.cad.plan_stats.get("imbalance_after"),
                           "planned_imbalance_before": trainer.cad.plan_stats.get("imbalance_before"),

@@ -185,7 +185,10 @@ template <typename GradT>
 __global__ void adam_kernel(__nv_bfloat16* __restrict__ param, short* __restrict__ lo16,
                             const GradT* __restrict__ grad, float* __restrict__ m, float* __restrict__ v,
                             long n, float lr, float beta1, float beta2, float eps, float wd, float bc1,
-                            float bc2, const float* __restrict__ gscale_ptr) {
+                            float bc2, const float* __restrict__ gscale_ptr,
+                            const unsigned int* __restrict__ status) {
+  // a step in which some kernel reported a failed wait or bounds check must not touch the weights
+  if (status != nullptr && *status != 0u) return;
   const float gs = gscale_ptr != nullptr ? gscale_ptr[0] : 1.f;
   for (long i = blockIdx.x * (long)blockDim.x + threadIdx.x; i < n; i += (long)gridDim.x * blockDim.x) {
     const uint32_t hi = (uint32_t)__bfloat16_as_ushort(param[i]) << 16;
@@ -215,7 +218,8 @@ adam_push_kernel(const __nv_bfloat16* __restrict__ param, short* __restrict__ lo
                  const __nv_bfloat16* __restrict__ grad, float* __restrict__ m, float* __restrict__ v, long n,
                  float lr, float beta1, float beta2, float eps, float wd, float bc1, float bc2,
                  const float* __restrict__ gscale_ptr, const unsigned long long* __restrict__ peer_param,
-                 int n_peers, long lo) {
+                 int n_peers, long lo, const unsigned int* __restrict__ status) {
+  if (status != nullptr && *status != 0u) return;   // see adam_kernel
   const float gs = gscale_ptr != nullptr ? gscale_ptr[0] : 1.f;
   const long nvec = n / 8;
   for (long i = blockIdx.x * (long)blockDim.x + threadIdx.x; i < nvec; i += (long)gridDim.x * blockDim.x) {
@@ -334,35 +338,38 @@ extern "C" int dca_sumsq(const void* g, int g_fp32, long n, float* sumsq, void* 
   return 0;
 }
 
+// `status` (may be null): the device status word; when it is non-zero the update is skipped, so a step whose
+// kernels reported a failed wait or bounds check leaves the weights and the optimizer state as they were.
 // AdamW + parameter all-gather in one kernel (bf16 gradients). param/lo16/grad/m/v: this rank's
 // shard (n elements, multiple of 8); peer_param: device array of n_peers addresses of the peers'
 // (and this rank's own) flat parameter buffers; lo: element offset of the shard in those buffers.
 extern "C" int dca_adam_push(const void* param, void* lo16, const void* grad, float* m, float* v, long n, float lr,
                              float beta1, float beta2, float eps, float wd, int step, const float* gscale_ptr,
-                             const void* peer_param, int n_peers, long lo, void* stream) {
+                             const void* peer_param, int n_peers, long lo, const unsigned int* status,
+                             void* stream) {
   if (n <= 0) return 0;
   if (n % 8 != 0 || lo % 8 != 0) return kErrBadArg;
   const float bc1 = 1.f - powf(beta1, (float)step);
   const float bc2 = 1.f - powf(beta2, (float)step);
   adam_push_kernel<<<grid_for(n / 8, 256), 256, 0, (cudaStream_t)stream>>>(
       (const __nv_bfloat16*)param, (short*)lo16, (const __nv_bfloat16*)grad, m, v, n, lr, beta1, beta2, eps, wd, bc1,
-      bc2, gscale_ptr, (const unsigned long long*)peer_param, n_peers, lo);
+      bc2, gscale_ptr, (const unsigned long long*)peer_param, n_peers, lo, status);
   DCA_CUDA_TRY(cudaGetLastError());
   return 0;
 }
 
 extern "C" int dca_adam(void* param, void* lo16, const void* grad, int g_fp32, float* m, float* v, long n,
                         float lr, float beta1, float beta2, float eps, float wd, int step,
-                        const float* gscale_ptr, void* stream) {
+                        const float* gscale_ptr, const unsigned int* status, void* stream) {
   if (n <= 0) return 0;
   const float bc1 = 1.f - powf(beta1, (float)step);
   const float bc2 = 1.f - powf(beta2, (float)step);
   if (g_fp32)
     adam_kernel<float><<<grid_for(n, 256), 256, 0, (cudaStream_t)stream>>>(
-        (__nv_bfloat16*)param, (short*)lo16, (const float*)grad, m, v, n, lr, beta1, beta2, eps, wd, bc1, bc2, gscale_ptr);
+        (__nv_bfloat16*)param, (short*)lo16, (const float*)grad, m, v, n, lr, beta1, beta2, eps, wd, bc1, bc2, gscale_ptr, status);
   else
     adam_kernel<__nv_bfloat16><<<grid_for(n, 256), 256, 0, (cudaStream_t)stream>>>(
-        (__nv_bfloat16*)param, (short*)lo16, (const __nv_bfloat16*)grad, m, v, n, lr, beta1, beta2, eps, wd, bc1, bc2, gscale_ptr);
+        (__nv_bfloat16*)param, (short*)lo16, (const __nv_bfloat16*)grad, m, v, n, lr, beta1, beta2, eps, wd, bc1, bc2, gscale_ptr, status);
   DCA_CUDA_TRY(cudaGetLastError());
   return 0;
 }

@@ -86,37 +86,43 @@ rmsnorm_fwd_kernel(const __nv_bfloat16* __restrict__ x, const __nv_bfloat16* __r
 }
 
 // dx = rstd * (dy*g - xhat * mean(dy*g*xhat)) [+ dres];  dg_partial[cta] = sum_rows dy * xhat
-__global__ void __launch_bounds__(kNormThreads)
+// NV = 16-byte vectors per thread (hidden size up to 256 * 8 * NV). The per-row critical path is
+// load -> block reduction -> store, so the kernel lives on occupancy: the weight is re-read from L1 every
+// row instead of being held in registers, the residual-gradient load is issued before the reduction, and
+// CTAS CTAs share an SM (measured at [131072, 4096]: 1 CTA per SM-half with everything in registers
+// reached 0.26 of the copy bandwidth).
+template <int NV, int CTAS>
+__global__ void __launch_bounds__(kNormThreads, CTAS)
 rmsnorm_bwd_kernel(const __nv_bfloat16* __restrict__ x, const __nv_bfloat16* __restrict__ g,
                    const float* __restrict__ rstd, const __nv_bfloat16* __restrict__ dy,
                    const __nv_bfloat16* __restrict__ dres, __nv_bfloat16* __restrict__ dx,
                    float* __restrict__ dg_partial, int T, int H) {
   __shared__ float scratch[32];
   const int nvec = H / 8;
-  float dg[kMaxVec][8];
-  float gv[kMaxVec][8];
+  float dg[NV][8];
 #pragma unroll
-  for (int i = 0; i < kMaxVec; ++i) {
-    const int v = threadIdx.x + i * kNormThreads;
+  for (int i = 0; i < NV; ++i) {
 #pragma unroll
     for (int j = 0; j < 8; ++j) dg[i][j] = 0.f;
-    if (v < nvec) load8(g + v * 8, gv[i]);
   }
   for (long row = blockIdx.x; row < T; row += gridDim.x) {
     const float r = rstd[row];
-    float xh[kMaxVec][8], dyg[kMaxVec][8];
+    float xh[NV][8], dyg[NV][8];
+    uint4 res[NV];
     float dot = 0.f;
 #pragma unroll
-    for (int i = 0; i < kMaxVec; ++i) {
+    for (int i = 0; i < NV; ++i) {
       const int v = threadIdx.x + i * kNormThreads;
       if (v < nvec) {
-        float xv[8], dv[8];
+        float xv[8], dv[8], gv[8];
         load8(x + row * H + v * 8, xv);
         load8(dy + row * H + v * 8, dv);
+        load8(g + v * 8, gv);
+        if (dres != nullptr) res[i] = *reinterpret_cast<const uint4*>(dres + row * H + v * 8);
 #pragma unroll
         for (int j = 0; j < 8; ++j) {
           xh[i][j] = xv[j] * r;
-          dyg[i][j] = dv[j] * gv[i][j];
+          dyg[i][j] = dv[j] * gv[j];
           dg[i][j] += dv[j] * xh[i][j];
           dot += dyg[i][j] * xh[i][j];
         }
@@ -124,30 +130,44 @@ rmsnorm_bwd_kernel(const __nv_bfloat16* __restrict__ x, const __nv_bfloat16* __r
     }
     dot = block_sum(dot, scratch) / (float)H;
 #pragma unroll
-    for (int i = 0; i < kMaxVec; ++i) {
+    for (int i = 0; i < NV; ++i) {
       const int v = threadIdx.x + i * kNormThreads;
       if (v < nvec) {
         float o[8];
 #pragma unroll
         for (int j = 0; j < 8; ++j) o[j] = r * (dyg[i][j] - xh[i][j] * dot);
         if (dres != nullptr) {
-          float rv[8];
-          load8(dres + row * H + v * 8, rv);
-#pragma unroll
-          for (int j = 0; j < 8; ++j) o[j] += rv[j];
+          const float2 a = unpack_bf16x2(res[i].x), b = unpack_bf16x2(res[i].y);
+          const float2 c = unpack_bf16x2(res[i].z), d = unpack_bf16x2(res[i].w);
+          o[0] += a.x; o[1] += a.y; o[2] += b.x; o[3] += b.y; o[4] += c.x; o[5] += c.y; o[6] += d.x; o[7] += d.y;
         }
         store8(dx + row * H + v * 8, o);
       }
     }
   }
 #pragma unroll
-  for (int i = 0; i < kMaxVec; ++i) {
+  for (int i = 0; i < NV; ++i) {
     const int v = threadIdx.x + i * kNormThreads;
     if (v < nvec) {
-#pragma unroll
-      for (int j = 0; j < 8; ++j) dg_partial[(long)blockIdx.x * H + v * 8 + j] = dg[i][j];
+      float4* dst = reinterpret_cast<float4*>(dg_partial + (long)blockIdx.x * H + v * 8);
+      dst[0] = make_float4(dg[i][0], dg[i][1], dg[i][2], dg[i][3]);
+      dst[1] = make_float4(dg[i][4], dg[i][5], dg[i][6], dg[i][7]);
     }
   }
+}
+
+// Launch with P CTAs (= rows of dg_partial), picking the vectors-per-thread variant for H.
+inline cudaError_t launch_rmsnorm_bwd(int P, cudaStream_t s, const __nv_bfloat16* x, const __nv_bfloat16* g,
+                                      const float* rstd, const __nv_bfloat16* dy, const __nv_bfloat16* dres,
+                                      __nv_bfloat16* dx, float* dg_partial, int T, int H) {
+  const int nv = (H / 8 + kNormThreads - 1) / kNormThreads;
+  if (nv <= 1)
+    rmsnorm_bwd_kernel<1, 4><<<P, kNormThreads, 0, s>>>(x, g, rstd, dy, dres, dx, dg_partial, T, H);
+  else if (nv <= 2)
+    rmsnorm_bwd_kernel<2, 4><<<P, kNormThreads, 0, s>>>(x, g, rstd, dy, dres, dx, dg_partial, T, H);
+  else
+    rmsnorm_bwd_kernel<4, 2><<<P, kNormThreads, 0, s>>>(x, g, rstd, dy, dres, dx, dg_partial, T, H);
+  return cudaGetLastError();
 }
 
 // dg[h] (+)= sum_p partial[p,h]   (dg bf16 or fp32)
@@ -240,7 +260,7 @@ extern "C" int dca_rmsnorm_fwd(const void* x, const void* g, void* y, float* rst
 
 // Number of CTAs (= rows of the dg_partial scratch) the backward kernel will use.
 extern "C" int dca_rmsnorm_bwd_partials(int T) {
-  int cap = sm_count() * 2;
+  int cap = sm_count() * 4;
   return T < cap ? (T > 0 ? T : 1) : cap;
 }
 
@@ -252,10 +272,9 @@ extern "C" int dca_rmsnorm_bwd(const void* x, const void* g, const float* rstd, 
   if (H % 8 != 0 || H > kNormThreads * 8 * kMaxVec) return kErrBadArg;
   const int P = dca_rmsnorm_bwd_partials(T);
   cudaStream_t s = (cudaStream_t)stream;
-  rmsnorm_bwd_kernel<<<P, kNormThreads, 0, s>>>(
-      (const __nv_bfloat16*)x, (const __nv_bfloat16*)g, rstd, (const __nv_bfloat16*)dy,
-      (const __nv_bfloat16*)dres, (__nv_bfloat16*)dx, dg_partial, T, H);
-  DCA_CUDA_TRY(cudaGetLastError());
+  DCA_CUDA_TRY(launch_rmsnorm_bwd(P, s, (const __nv_bfloat16*)x, (const __nv_bfloat16*)g, rstd,
+                                  (const __nv_bfloat16*)dy, (const __nv_bfloat16*)dres, (__nv_bfloat16*)dx,
+                                  dg_partial, T, H));
   if (dg_fp32)
     rmsnorm_dg_reduce_kernel<float><<<(H + 127) / 128, 128, 0, s>>>(dg_partial, (float*)dg, P, H, dg_accumulate);
   else
@@ -312,10 +331,9 @@ extern "C" int dca_rmsnorm_bwd_noalloc(const void* x, const void* g, const float
   }
   float* partial = g_noalloc_ptr[dev];
   cudaStream_t s = (cudaStream_t)stream;
-  rmsnorm_bwd_kernel<<<P, kNormThreads, 0, s>>>(
-      (const __nv_bfloat16*)x, (const __nv_bfloat16*)g, rstd, (const __nv_bfloat16*)dy,
-      (const __nv_bfloat16*)dres, (__nv_bfloat16*)dx, partial, T, H);
-  DCA_CUDA_TRY(cudaGetLastError());
+  DCA_CUDA_TRY(launch_rmsnorm_bwd(P, s, (const __nv_bfloat16*)x, (const __nv_bfloat16*)g, rstd,
+                                  (const __nv_bfloat16*)dy, (const __nv_bfloat16*)dres, (__nv_bfloat16*)dx,
+                                  partial, T, H));
   if (dg_fp32)
     rmsnorm_dg_reduce_kernel<float><<<(H + 127) / 128, 128, 0, s>>>(partial, (float*)dg, P, H, dg_accumulate);
   else

@@ -23,6 +23,8 @@ struct RopeParams {
   __nv_bfloat16* qkv;        // in place when no destinations are given
   const int* pos;            // [T] position of each token inside its document
   const float* cos_sin;      // [max_pos, D]
+  int max_pos;               // rows of cos_sin; a position beyond it is clamped and reported in the status word
+  unsigned int* status;
   long T;
   int heads_q, heads_kv, D;
   long ld;                   // row pitch of qkv in elements
@@ -46,7 +48,13 @@ rope_kernel(const RopeParams p) {
   const int items = items_rot + (scatter ? v_vecs : 0);
   for (long t = blockIdx.x; t < p.T; t += gridDim.x) {
     __nv_bfloat16* row = p.qkv + t * p.ld;
-    const float* cs = p.cos_sin + (long)p.pos[t] * p.D;
+    int ps = p.pos[t];
+    if (ps < 0 || ps >= p.max_pos) {
+      // never read past the table: rotate by the last row and report (the host raises on the status word)
+      if (threadIdx.x == 0 && p.status != nullptr) atomicCAS(p.status, 0u, (unsigned int)kStatusBounds);
+      ps = ps < 0 ? 0 : p.max_pos - 1;
+    }
+    const float* cs = p.cos_sin + (long)ps * p.D;
     const unsigned long long qd = scatter ? p.q_dst[t] : 0ull;
     for (int it = threadIdx.x; it < items; it += blockDim.x) {
       if (it < items_rot) {
@@ -114,15 +122,17 @@ rope_kernel(const RopeParams p) {
 
 using namespace dca;
 
-extern "C" int dca_rope(void* qkv, const int* pos, const float* cos_sin, long T, int heads_q, int heads_kv,
-                        int D, long ld, int backward, const void* q_dst, const void* kv_dst, int max_copies,
-                        long v_off_bytes, int write_inplace, void* stream) {
+extern "C" int dca_rope(void* qkv, const int* pos, const float* cos_sin, int max_pos, long T, int heads_q,
+                        int heads_kv, int D, long ld, int backward, const void* q_dst, const void* kv_dst,
+                        int max_copies, long v_off_bytes, int write_inplace, unsigned int* status, void* stream) {
   if (T <= 0) return 0;
-  if (D % 16 != 0 || ld % 8 != 0) return kErrBadArg;
+  if (D % 16 != 0 || ld % 8 != 0 || max_pos <= 0) return kErrBadArg;
   rope::RopeParams p;
   p.qkv = (__nv_bfloat16*)qkv;
   p.pos = pos;
   p.cos_sin = cos_sin;
+  p.max_pos = max_pos;
+  p.status = status;
   p.T = T;
   p.heads_q = heads_q; p.heads_kv = heads_kv; p.D = D; p.ld = ld;
   p.sign = backward ? -1.f : 1.f;

@@ -59,6 +59,7 @@ struct Params {
   // EPI_ROPE (QKV projection, head_dim 128: an N tile is two heads)
   const int* rope_pos;               // [M] position of each token inside its document
   const float* rope_table;           // [max_pos, 128] = (cos[0..64) | sin[0..64))
+  int rope_max_pos;                  // rows of rope_table; positions beyond it are clamped and reported
   int heads_q, heads_kv;             // heads in this GEMM's N dimension: Q heads, then K, then V
   const unsigned long long* q_dst;   // [M] destination address of the token's Q row (0 = none), or null
   const unsigned long long* kv_dst;  // [M, max_copies] destination addresses of its K row (0 ends the list)
@@ -320,7 +321,13 @@ gemm_bf16_kernel(const __grid_constant__ TmapSet<NA> tmAs, const __grid_constant
         }
       } else if (p.epi == EPI_ROPE) {
         // Two heads of 128 per tile. Rotation pairs are (i, i + 64): TMEM chunks (0, 2) and (1, 3).
-        const float* cs = p.rope_table + (long)(row_ok ? p.rope_pos[row] : 0) * 128;
+        int ps = row_ok ? p.rope_pos[row] : 0;
+        if (ps < 0 || ps >= p.rope_max_pos) {
+          // never read past the table: rotate by an in-range row and report through the status word
+          if (p.status != nullptr) atomicCAS(p.status, 0u, (unsigned int)kStatusBounds);
+          ps = ps < 0 ? 0 : p.rope_max_pos - 1;
+        }
+        const float* cs = p.rope_table + (long)ps * 128;
         const unsigned long long qd = (p.q_dst != nullptr && row_ok) ? p.q_dst[row] : 0ull;
         __nv_bfloat16* crow = p.C != nullptr ? reinterpret_cast<__nv_bfloat16*>(p.C) + row * p.ldc : nullptr;
 #pragma unroll 1
@@ -487,6 +494,7 @@ int launch(const TmapSet<NA>& tmA, const CUtensorMap& tmB, const Params& p, int 
 struct RopeArgs {
   const int* pos = nullptr;
   const float* table = nullptr;
+  int max_pos = 0;
   int heads_q = 0, heads_kv = 0;
   const unsigned long long* q_dst = nullptr;
   const unsigned long long* kv_dst = nullptr;
@@ -544,14 +552,14 @@ static int gemm_impl(const void* A, const void* B, void* C, int M, int N, int K,
   p.epi = epi; p.F = N / 2; p.preact = preact; p.ld_preact = ld_preact;
   p.group_m = 16;
   p.status = status;
-  p.rope_pos = nullptr; p.rope_table = nullptr; p.heads_q = p.heads_kv = 0;
+  p.rope_pos = nullptr; p.rope_table = nullptr; p.rope_max_pos = 0; p.heads_q = p.heads_kv = 0;
   p.q_dst = p.kv_dst = nullptr; p.max_copies = 0; p.v_off_bytes = 0;
   if (epi == dca::gemm::EPI_ROPE) {
     if (rope == nullptr || rope->pos == nullptr || rope->table == nullptr || out_fp32 || accumulate ||
         residual != nullptr || n_c_peers > 0 || (N % 128) != 0 || (rope->heads_q + 2 * rope->heads_kv) * 128 != N ||
-        (C == nullptr && rope->q_dst == nullptr))
+        (C == nullptr && rope->q_dst == nullptr) || rope->max_pos <= 0)
       return kErrBadArg;
-    p.rope_pos = rope->pos; p.rope_table = rope->table; p.heads_q = rope->heads_q; p.heads_kv = rope->heads_kv;
+    p.rope_pos = rope->pos; p.rope_table = rope->table; p.rope_max_pos = rope->max_pos; p.heads_q = rope->heads_q; p.heads_kv = rope->heads_kv;
     p.q_dst = rope->q_dst; p.kv_dst = rope->kv_dst; p.max_copies = rope->max_copies; p.v_off_bytes = rope->v_off_bytes;
   }
   p.a_rows_per_peer = n_a_peers > 1 ? (int)a_rows_per_peer : 0;
@@ -592,16 +600,16 @@ extern "C" int dca_gemm_bf16_tp(const void* A, const void* B, void* C, int M, in
 
 // QKV projection with RoPE and the core-attention dispatch in the epilogue (head_dim 128).
 // N = (heads_q + 2 * heads_kv) * 128, Q heads first, then K, then V. `pos` [M] int32, `table` fp32
-// [max_pos, 128] (cos | sin). C (may be null when destinations are given) receives the rotated rows;
+// [max_pos, 128] (cos | sin); a position outside [0, max_pos) is clamped and sets the status word. C (may be null when destinations are given) receives the rotated rows;
 // q_dst [M] / kv_dst [M, max_copies] (may be null) are destination addresses as in dca_rope.
 // a_peers / n_a_peers / a_rows_per_peer as in dca_gemm_bf16_tp (0 peers: A is used).
 extern "C" int dca_gemm_qkv_rope(const void* A, const void* B, void* C, int M, int N, int K, long lda, long ldb,
-                                 long ldc, const int* pos, const float* table, int heads_q, int heads_kv,
-                                 const void* q_dst, const void* kv_dst, int max_copies, long v_off_bytes,
+                                 long ldc, const int* pos, const float* table, int max_pos, int heads_q,
+                                 int heads_kv, const void* q_dst, const void* kv_dst, int max_copies, long v_off_bytes,
                                  const void* const* a_peers, int n_a_peers, long a_rows_per_peer,
                                  unsigned int* status, void* stream) {
   RopeArgs r;
-  r.pos = pos; r.table = table; r.heads_q = heads_q; r.heads_kv = heads_kv;
+  r.pos = pos; r.table = table; r.max_pos = max_pos; r.heads_q = heads_q; r.heads_kv = heads_kv;
   r.q_dst = (const unsigned long long*)q_dst; r.kv_dst = (const unsigned long long*)kv_dst;
   r.max_copies = max_copies; r.v_off_bytes = v_off_bytes;
   return gemm_impl(A, B, C, M, N, K, lda, ldb, ldc, 0, 0, 0, 0, dca::gemm::EPI_ROPE, nullptr, 0, nullptr, 0,

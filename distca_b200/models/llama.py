@@ -600,6 +600,20 @@ class LlamaModel:
             self._store.never_asked = cfg.num_layers - (nl - 1)
         return self._store
 
+    def ensure_positions(self, longest_document: int) -> None:
+        """Make sure the rotary table covers positions ``0 .. longest_document - 1``. A configuration whose
+        ``max_position`` is shorter than the documents it is trained on (a Hugging Face config with
+        ``max_position_embeddings`` 8192 and 128K-token documents, or documents elongated beyond the preset)
+        gets a longer table here, before any kernel indexes it; the kernels themselves clamp and report
+        an out-of-range position instead of reading past the table."""
+        if longest_document > self.rope_table.shape[0]:
+            rows = 1 << max(0, int(longest_document - 1)).bit_length()
+            import logging
+            logging.getLogger("distca_b200").warning(
+                "documents of %d tokens exceed max_position %d: rotary table extended to %d rows",
+                longest_document, self.rope_table.shape[0], rows)
+            self.rope_table = ew.rope_table(rows, self.cfg.head_dim, self.cfg.rope_theta, self.device)
+
     def load_full_state(self, full: dict) -> None:
         """Load un-sharded tensors (this repository's row order), slicing for this tensor-parallel rank."""
         for name, _ in self.store.shapes:

@@ -34,8 +34,10 @@ def lib() -> ctypes.CDLL:
     """Load (building first if the sources are newer and nvcc exists) the kernel library."""
     global _LIB
     if _LIB is None:
-        path = _ROOT / "_kernels.so"
-        if not path.exists() or os.environ.get("DISTCA_REBUILD", "0") == "1":
+        path = Path(os.environ["DISTCA_KERNELS_SO"]) if os.environ.get("DISTCA_KERNELS_SO") else _ROOT / "_kernels.so"
+        if os.environ.get("DISTCA_KERNELS_SO"):
+            pass        # an explicitly named build of the same sources (e.g. with other -D switches): never rebuilt here
+        elif not path.exists() or os.environ.get("DISTCA_REBUILD", "0") == "1":
             from .. import build
             build.build_kernels()
         if not path.exists():

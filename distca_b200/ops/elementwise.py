@@ -152,11 +152,12 @@ def rope_(qkv: torch.Tensor, pos: torch.Tensor, table: torch.Tensor, heads_q: in
         qkv[:, :n_rot * D] = out.reshape(T, n_rot * D).to(qkv.dtype)
         return qkv
     assert pos.dtype == torch.int32 and table.dtype == torch.float32 and table.shape[1] == D
-    rc = _lib.lib().dca_rope(_lib.ptr(qkv), _lib.ptr(pos), _lib.ptr(table), _lib.c_long(T), _lib.c_int(heads_q),
-                             _lib.c_int(heads_kv), _lib.c_int(D), _lib.c_long(qkv.stride(0)),
+    rc = _lib.lib().dca_rope(_lib.ptr(qkv), _lib.ptr(pos), _lib.ptr(table), _lib.c_int(table.shape[0]), _lib.c_long(T),
+                             _lib.c_int(heads_q), _lib.c_int(heads_kv), _lib.c_int(D), _lib.c_long(qkv.stride(0)),
                              _lib.c_int(1 if backward else 0), _lib.ptr(q_dst), _lib.ptr(kv_dst),
                              _lib.c_int(max_copies), _lib.c_long(v_off_bytes),
-                             _lib.c_int(1 if write_inplace else 0), _lib.stream_ptr())
+                             _lib.c_int(1 if write_inplace else 0), _lib.ptr(_lib.status_word(qkv.device)),
+                             _lib.stream_ptr())
     _lib.check_rc(rc, "rope")
     return qkv
 
@@ -299,7 +300,7 @@ def adam_step_(param: torch.Tensor, lo16: torch.Tensor, grad: torch.Tensor, m: t
                              _lib.c_int(1 if grad.dtype == torch.float32 else 0), _lib.ptr(m), _lib.ptr(v),
                              _lib.c_long(n), _lib.c_float(lr), _lib.c_float(beta1), _lib.c_float(beta2),
                              _lib.c_float(eps), _lib.c_float(weight_decay), _lib.c_int(step), _lib.ptr(gscale),
-                             _lib.stream_ptr())
+                             _lib.ptr(_lib.status_word(param.device)), _lib.stream_ptr())
     _lib.check_rc(rc, "adam")
 
 

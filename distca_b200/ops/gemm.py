@@ -154,8 +154,8 @@ def linear_qkv_rope(x: torch.Tensor, w: torch.Tensor, pos: torch.Tensor, table: 
     out = torch.empty(T, N, dtype=torch.bfloat16, device=w.device) if write_local else None
     rc = _lib.lib().dca_gemm_qkv_rope(
         a_ptr, _lib.ptr(w), _lib.ptr(out), _lib.c_int(T), _lib.c_int(N), _lib.c_int(K), _lib.c_long(lda),
-        _lib.c_long(w.stride(0)), _lib.c_long(N), _lib.ptr(pos), _lib.ptr(table), _lib.c_int(heads_q),
-        _lib.c_int(heads_kv), _lib.ptr(q_dst), _lib.ptr(kv_dst), _lib.c_int(max_copies), _lib.c_long(v_off_bytes),
+        _lib.c_long(w.stride(0)), _lib.c_long(N), _lib.ptr(pos), _lib.ptr(table), _lib.c_int(table.shape[0]),
+        _lib.c_int(heads_q), _lib.c_int(heads_kv), _lib.ptr(q_dst), _lib.ptr(kv_dst), _lib.c_int(max_copies), _lib.c_long(v_off_bytes),
         a_peers, _lib.c_int(n_peers), _lib.c_long(a_rows_per_peer), _lib.ptr(_lib.status_word(w.device)),
         _lib.stream_ptr())
     _lib.check_rc(rc, "gemm_qkv_rope")

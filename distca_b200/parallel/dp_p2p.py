@@ -48,7 +48,7 @@ class PeerDataParallel:
                                       _lib.c_long(pshard.numel()), _lib.c_float(lr), _lib.c_float(beta1),
                                       _lib.c_float(beta2), _lib.c_float(eps), _lib.c_float(weight_decay), _lib.c_int(step),
                                       _lib.ptr(gscale), _lib.ptr(self.param_tbl), _lib.c_int(self.size), _lib.c_long(lo),
-                                      _lib.stream_ptr())
+                                      _lib.ptr(_lib.status_word(pshard.device)), _lib.stream_ptr())
         _lib.check_rc(rc, "adam_push")
         self.sig.signal(1)      # my shard has been stored everywhere, and I no longer read peers' gradients
         self.sig.wait(1)        # everybody's shard has arrived here; peers are done with my gradient buffer

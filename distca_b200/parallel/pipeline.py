@@ -73,6 +73,8 @@ class PipelineTrainer:
         self.next = par.rank_of(self.tp_rank, self.dp_rank, self.pp_rank + 1) if not self.last else None
         self.act_dtype = self.model.dtype
         self.step_idx = 0
+        from ..utils.watchdog import StepGuard
+        self.guard = StepGuard.for_process_group()     # heartbeat check before, watchdog around every step
 
     # ------------------------------------------------------------------------------------------
     def _exchange(self, send_next=None, send_prev=None, recv_prev_shape=None, recv_next_shape=None):
@@ -114,7 +116,13 @@ class PipelineTrainer:
     # ------------------------------------------------------------------------------------------
     def train_step(self, hb) -> float:
         """``hb``: HostBatch whose tensors hold ``M`` micro-batches of equal length back to back;
-        ``hb.all_doc_lens[d]`` lists rank d's documents of all micro-batches in order."""
+        ``hb.all_doc_lens[d]`` lists rank d's documents of all micro-batches in order. A lost peer raises on
+        the host before anything is launched; the step runs under the watchdog."""
+        self.guard.check()
+        with self.guard.watch("pipeline step"):
+            return self._train_step(hb)
+
+    def _train_step(self, hb) -> float:
         M, pp, p = self.M, self.par.pp, self.pp_rank
         self.model.store.zero_grad()
         T, all_mb_docs, batches = self._split_microbatches(hb)
@@ -166,11 +174,14 @@ class PipelineTrainer:
         dist.all_reduce(loss_sum, group=self.groups.world_group)
         loss_sum /= self.par.tp
         self.step_idx += 1
-        return float(loss_sum.item())
+        value = float(loss_sum.item())
+        self.check_device_status()      # raises when a kernel of this step reported a failed wait / bounds check
+        return value
 
     def _split_microbatches(self, hb):
         M = self.M
         T = hb.ids.numel() // M
+        self.model.ensure_positions(max(hb.doc_lens, default=0))
         all_mb_docs = [[[] for _ in range(self.par.dp)] for _ in range(M)]
         for d, docs in enumerate(hb.all_doc_lens):
             acc, mb = 0, 0
@@ -223,6 +234,7 @@ class PipelineTrainer:
             _lib.check_status(self.device, "pipeline step")
 
     def close(self) -> None:
+        self.guard.close()
         if self.cad is not None:
             self.cad.close()
             self.cad = None

@@ -214,6 +214,8 @@ class Trainer:
                                replicated_names=repl if par.tp > 1 else (), tp_rank=self.tp_rank, p2p=self.p2p)
         self.step_idx = 0
         self.timers: dict[str, float] = {}
+        from ..utils.watchdog import StepGuard
+        self.guard = StepGuard.for_process_group()     # heartbeat check before, watchdog around every step
         self._plan_pool = None       # worker thread that plans the next step's core attention
         self._plan_ahead = None      # (document lists, Future of the plan)
 
@@ -286,9 +288,17 @@ class Trainer:
                 ca.set_batch(AttnPlan(AttnTasks.from_doc_lens(hb.doc_lens), self.device))
 
     def train_step(self, hb) -> float:
+        """One optimizer step on ``hb`` (host tensors); returns the loss. Before anything is launched the
+        peers' heartbeats are checked (a lost rank raises on the host), and the step runs under a watchdog."""
+        self.guard.check()
+        with self.guard.watch():
+            return self._train_step(hb)
+
+    def _train_step(self, hb) -> float:
         from ..utils import timers
         with timers.phase("zero_grad"):
             self.model.store.zero_grad()
+        self.model.ensure_positions(max(hb.doc_lens, default=0))
         if isinstance(hb, SpanHostBatch):
             # documents may span ranks: the planner decides the layout, then this rank cuts out its tokens
             assert self.cad is not None and self.nano == 1, "spanning documents need core-attention disaggregation"
@@ -323,12 +333,18 @@ class Trainer:
         if self.groups is not None and self.par.dp > 1:
             dist.all_reduce(loss, group=self.groups.dp_group)
         self.step_idx += 1
-        return float(loss.item())
+        value = float(loss.item())
+        # the read above synchronised: a wait that ran out or a failed bounds check in this step raises here,
+        # before the caller logs the loss, checkpoints or starts another step (the Adam kernels of such a
+        # step have already skipped their update)
+        self.check_device_status()
+        return value
 
     def train_step_prepared(self, batch: Batch, hb: HostBatch) -> torch.Tensor:
         """Same step with the batch already on the device and the plan built; returns the loss as a
         device tensor (no host synchronisation). Used for device-only timing."""
         self.model.store.zero_grad()
+        self.model.ensure_positions(max(hb.doc_lens, default=0))
         if self.nano == 2:
             loss, _ = self.model.forward_backward_nano(batch, self.core_attns)   # batch: list of nano-batches
         else:
@@ -340,6 +356,7 @@ class Trainer:
         return loss
 
     def eval_step(self, hb: HostBatch) -> float:
+        self.model.ensure_positions(max(hb.doc_lens, default=0))
         batch = self.to_device(hb)
         self.plan_attention(hb)
         loss = self.model.forward_loss(batch, self.core_attn)
@@ -356,6 +373,7 @@ class Trainer:
         if self._plan_pool is not None:
             self._plan_pool.shutdown(wait=True)
             self._plan_pool = None
+        self.guard.close()
         if self.cad is not None:
             for ca in self.core_attns:
                 ca.close()

@@ -70,3 +70,75 @@ class Heartbeat:
             elif now - last[1] > stale_after_s:
                 dead.append(r)
         return dead
+
+    # ---- background beating: proves the PROCESS is alive while a long step runs ----
+    def start(self, interval_s: float = 0.5) -> None:
+        """Beat from a daemon thread every ``interval_s`` seconds until :meth:`stop` (or process exit)."""
+        if getattr(self, "_thread", None) is not None:
+            return
+        self._stop = threading.Event()
+
+        def run():
+            while not self._stop.wait(interval_s):
+                try:
+                    self.beat()
+                except Exception:       # the store went away (job shutting down)
+                    return
+        self.beat()
+        self._thread = threading.Thread(target=run, name="distca-heartbeat", daemon=True)
+        self._thread.start()
+
+    def stop(self) -> None:
+        if getattr(self, "_thread", None) is not None:
+            self._stop.set()
+            self._thread.join(timeout=2.0)
+            self._thread = None
+
+
+class RankLost(RuntimeError):
+    """Raised on the host, before the next launch, when another rank's heartbeat stopped."""
+
+
+class StepGuard:
+    """What both trainers put around every step: ``check()`` before anything is launched (raises
+    :class:`RankLost` when a peer's heartbeat has stopped, so no kernel ever waits on the device for a rank
+    that is gone) and ``watch()`` around the step (a step that exceeds the deadline dumps all Python stacks
+    and ends the process with exit code 3). Heartbeats use the process group's own store; with a single
+    process only the watchdog is active.
+
+    Environment: ``DISTCA_STEP_TIMEOUT_S`` (default 3600), ``DISTCA_HEARTBEAT_STALE_S`` (default 10, 0 = off).
+    """
+
+    def __init__(self, rank: int = 0, world: int = 1, store=None, step_timeout_s: float | None = None,
+                 stale_after_s: float | None = None, on_timeout=None, beat_interval_s: float = 0.5):
+        self.step_timeout_s = float(os.environ.get("DISTCA_STEP_TIMEOUT_S", 3600.0)) if step_timeout_s is None else step_timeout_s
+        self.stale_after_s = float(os.environ.get("DISTCA_HEARTBEAT_STALE_S", 10.0)) if stale_after_s is None else stale_after_s
+        self.on_timeout = on_timeout
+        self.hb = None
+        if world > 1 and store is not None and self.stale_after_s > 0:
+            self.hb = Heartbeat(store, rank, world, prefix="distca_hb")
+            self.hb.start(beat_interval_s)
+            self.hb.dead_ranks(self.stale_after_s)      # first observation of every peer's counter
+
+    @staticmethod
+    def for_process_group(**kw) -> "StepGuard":
+        """Guard over the default process group's store (single process: watchdog only)."""
+        import torch.distributed as dist
+        if not dist.is_initialized() or dist.get_world_size() == 1:
+            return StepGuard(**kw)
+        from torch.distributed.distributed_c10d import _get_default_store
+        return StepGuard(dist.get_rank(), dist.get_world_size(), _get_default_store(), **kw)
+
+    def check(self) -> None:
+        if self.hb is not None:
+            dead = self.hb.dead_ranks(self.stale_after_s)
+            if dead:
+                raise RankLost(f"ranks {dead} stopped sending heartbeats: not launching the next step")
+
+    def watch(self, what: str = "training step") -> StepWatchdog:
+        return StepWatchdog(self.step_timeout_s, what, self.on_timeout)
+
+    def close(self) -> None:
+        if self.hb is not None:
+            self.hb.stop()
+            self.hb = None

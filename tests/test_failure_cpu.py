@@ -109,3 +109,70 @@ def test_plan_that_cannot_fit_is_reported():
     p = Planner(PlannerConfig(world=2, tokens_per_rank=8192, max_q_rows=100, max_kv_rows=100))
     plan = p.plan_fixed([[8192], [4096, 4096]])
     assert not plan.fits
+
+
+def _guard_worker(rank, world, port, q):
+    """Two ranks train one step together; rank 1 then stops (its heartbeat thread ends, as when the process
+    dies between steps). Rank 0's next ``train_step`` must raise on the host before launching anything."""
+    try:
+        os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port), RANK=str(rank), WORLD_SIZE=str(world),
+                          LOCAL_RANK=str(rank), DISTCA_HEARTBEAT_STALE_S="1.0")
+        dist.init_process_group("gloo", rank=rank, world_size=world, timeout=datetime.timedelta(seconds=30))
+        from distca_b200.models.config import PRESETS, ParallelConfig, TrainConfig
+        from distca_b200.runtime.trainer import BatchSource, Trainer
+        from distca_b200.utils.watchdog import RankLost
+        cfg = PRESETS["tiny"]
+        par = ParallelConfig(tp=1, pp=1, dp=2)
+        tr = Trainer(cfg, par, TrainConfig(cad=True, recompute="full", lm_head_chunk=2048), device="cpu", seed=0)
+        src = BatchSource(cfg, par, 1024, "loguniform64", seed=0, pinned=False)
+        loss = tr.train_step(src.next(tr.dp_rank))
+        assert loss == loss
+        if rank == 1:
+            tr.guard.close()             # "dies" between steps: no kernel or collective of its own in flight
+            q.put((rank, "left"))
+            time.sleep(6)
+            return
+        t0 = time.time()
+        res = "no error"
+        while time.time() - t0 < 10.0:
+            try:
+                tr.guard.check()
+            except RankLost:
+                break
+            time.sleep(0.2)
+        try:
+            tr.train_step(src.next(tr.dp_rank))
+        except RankLost as e:
+            res = ("rank lost", time.time() - t0, str(e))
+        q.put((rank, res))
+    except Exception as e:  # pragma: no cover
+        import traceback
+        q.put((rank, repr(e) + traceback.format_exc()))
+
+
+def test_trainer_refuses_next_step_when_a_peer_stopped():
+    ctx = mp.get_context("spawn")
+    q = ctx.Queue()
+    port = _free_port()
+    procs = [ctx.Process(target=_guard_worker, args=(r, 2, port, q)) for r in range(2)]
+    for p in procs:
+        p.start()
+    res = dict(q.get(timeout=120) for _ in range(2))
+    for p in procs:
+        p.join(timeout=30)
+        if p.is_alive():
+            p.kill()
+    assert res[1] == "left"
+    assert res[0][0] == "rank lost" and "[1]" in res[0][2], res[0]
+
+
+def test_step_guard_watchdog_fires_inside_trainer_step():
+    """The watchdog that both trainers arm around a step: a step that overruns calls the timeout hook."""
+    from distca_b200.utils.watchdog import StepGuard
+    hit = []
+    g = StepGuard(step_timeout_s=0.2, on_timeout=lambda: hit.append(1))
+    with g.watch():
+        time.sleep(0.5)
+    assert hit == [1]
+    g.check()          # single process: nothing to check, must not raise
+    g.close()

@@ -72,3 +72,26 @@ def test_hf_config_mapping_llama_and_qwen2():
     qwen = ModelConfig.from_hf({**base, "architectures": ["Qwen2ForCausalLM"], "tie_word_embeddings": True})
     assert not llama.qkv_bias and qwen.qkv_bias and qwen.tie_embeddings and llama.head_dim == 64
     assert qwen.num_params() == llama.num_params() + 4 * llama.qkv_dim - 1000 * 512
+
+
+def test_rotary_table_grows_for_documents_longer_than_max_position():
+    """The host guard in front of the RoPE kernels: a document longer than the configuration's
+    ``max_position`` extends the table before anything indexes it, and the result equals a model that
+    was configured with the longer table from the start."""
+    kw = dict(name="t", num_layers=1, hidden=32, heads_q=2, heads_kv=1, head_dim=16, ffn=48, vocab=64)
+    short = LlamaModel(ModelConfig(max_position=32, **kw), "cpu", dtype=torch.float64)
+    long_ = LlamaModel(ModelConfig(max_position=128, **kw), "cpu", dtype=torch.float64)
+    assert short.rope_table.shape[0] == 32
+    short.ensure_positions(20)
+    assert short.rope_table.shape[0] == 32           # still fits: untouched
+    short.ensure_positions(100)
+    assert short.rope_table.shape[0] == 128
+    torch.testing.assert_close(short.rope_table, long_.rope_table)
+    doc_lens = [100, 12]
+    batch = _batch(short.cfg, doc_lens)
+    losses = []
+    for m in (short, long_):
+        ca = LocalCoreAttention(m.cfg)
+        ca.set_batch(AttnPlan(AttnTasks.from_doc_lens(doc_lens), "cpu", need_backward=False))
+        losses.append(m.forward_loss(batch, ca).item())
+    assert abs(losses[0] - losses[1]) < 1e-9
