@@ -66,6 +66,15 @@ PYBIND11_MODULE(_planner, m) {
       .def_readwrite("q_row_bytes", &ModelDims::q_row_bytes)
       .def_readwrite("kv_row_bytes", &ModelDims::kv_row_bytes);
 
+  py::class_<CostModel>(m, "CostModel")
+      .def(py::init<>())
+      .def_readwrite("enabled", &CostModel::enabled)
+      .def_readwrite("tile", &CostModel::tile)
+      .def_readwrite("ms_per_tile_pair", &CostModel::ms_per_tile_pair)
+      .def_readwrite("ms_per_q_tile", &CostModel::ms_per_q_tile)
+      .def_readwrite("ms_per_task", &CostModel::ms_per_task)
+      .def("chunk_ms", &CostModel::chunk_ms);
+
   py::class_<PlannerOptions>(m, "PlannerOptions")
       .def(py::init<>())
       .def_readwrite("world", &PlannerOptions::world)
@@ -74,7 +83,9 @@ PYBIND11_MODULE(_planner, m) {
       .def_readwrite("dims", &PlannerOptions::dims)
       .def_readwrite("max_q_rows", &PlannerOptions::max_q_rows)
       .def_readwrite("max_kv_rows", &PlannerOptions::max_kv_rows)
-      .def_readwrite("per_task_overhead_flops", &PlannerOptions::per_task_overhead_flops);
+      .def_readwrite("per_task_overhead_flops", &PlannerOptions::per_task_overhead_flops)
+      .def_readwrite("cost", &PlannerOptions::cost)
+      .def_readwrite("speed", &PlannerOptions::speed);
 
   py::class_<RankPlan>(m, "RankPlan")
       .def_readonly("num_tokens", &RankPlan::num_tokens)
@@ -98,6 +109,8 @@ PYBIND11_MODULE(_planner, m) {
       .def_readonly("flops_after", &Plan::flops_after)
       .def_readonly("imbalance_before", &Plan::imbalance_before)
       .def_readonly("imbalance_after", &Plan::imbalance_after)
+      .def_readonly("cost_after", &Plan::cost_after)
+      .def_readonly("cost_imbalance_after", &Plan::cost_imbalance_after)
       .def_readonly("fits", &Plan::fits)
       .def_property_readonly("items", [](const Plan& p) { return items_to_list(p.items); })
       .def("rank", [](const Plan& p, int r) -> const RankPlan& { return p.ranks.at(r); },

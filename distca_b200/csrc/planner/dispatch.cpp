@@ -38,6 +38,7 @@ Plan compile_plan(const std::vector<Item>& layout_items, const std::vector<Item>
   plan.ranks.resize(W);
   plan.flops_before.assign(W, 0.0);
   plan.flops_after.assign(W, 0.0);
+  plan.cost_after.assign(W, 0.0);
   for (const auto& it : layout_items) plan.flops_before[it.dst] += it.flops();
 
   // ---- owner side: local layout (rows -> document ranges) ----
@@ -60,6 +61,7 @@ Plan compile_plan(const std::vector<Item>& layout_items, const std::vector<Item>
   std::vector<std::vector<Chunk>> per_server(W);
   for (const auto& it : balanced) {
     plan.flops_after[it.dst] += it.flops();
+    plan.cost_after[it.dst] += opt.item_cost(it);
     if (it.head.len() > 0) per_server[it.dst].push_back({it.doc, it.head.a, it.head.b, it.src, it.head_row0});
     if (it.tail.len() > 0) per_server[it.dst].push_back({it.doc, it.tail.a, it.tail.b, it.src, it.tail_row0});
   }
@@ -187,6 +189,19 @@ Plan compile_plan(const std::vector<Item>& layout_items, const std::vector<Item>
   }
   plan.imbalance_before = max_over_mean(plan.flops_before);
   plan.imbalance_after = max_over_mean(plan.flops_after);
+  {
+    // cost of every server against ITS share of the total (equal shares unless speeds are given)
+    double total = 0.0, ssum = 0.0;
+    for (double c : plan.cost_after) total += c;
+    const bool weighted = (int)opt.speed.size() == W;
+    for (int r = 0; r < W; ++r) ssum += weighted ? std::max(opt.speed[r], 0.0) : 1.0;
+    double worst = 0.0;
+    for (int r = 0; r < W; ++r) {
+      const double share = total * (weighted ? std::max(opt.speed[r], 0.0) : 1.0) / (ssum > 0 ? ssum : 1.0);
+      if (share > 0) worst = std::max(worst, plan.cost_after[r] / share);
+    }
+    plan.cost_imbalance_after = total > 0 ? worst : 1.0;
+  }
   return plan;
 }
 

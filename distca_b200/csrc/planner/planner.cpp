@@ -26,6 +26,38 @@ double Item::flops() const {
   return f;
 }
 
+// Tile pairs the attention kernels visit for a chunk: query tile i (rows [i*T, min((i+1)*T, q))) sees the keys
+// [0, kv - q + min((i+1)*T, q)), i.e. ceil(.../T) key tiles; the diagonal tile counts whole.
+static inline double chunk_tile_pairs(int q, int kv, int T) {
+  if (q <= 0) return 0.0;
+  const long nq = (q + T - 1) / T;
+  const long base_tiles = ((long)(kv - q) + T - 1) / T;          // ceil((kv - q) / T)
+  // tiles i < nq - 1 are full: (i + 1) + ceil((kv - q) / T) key tiles each; the last one reaches kv
+  const double full = (double)(nq - 1) * nq / 2.0 + (double)(nq - 1) * base_tiles;
+  return full + (double)(((long)kv + T - 1) / T);
+}
+
+double CostModel::chunk_ms(int q, int kv) const {
+  if (q <= 0) return 0.0;
+  const double nq = (double)((q + tile - 1) / tile);
+  return ms_per_tile_pair * chunk_tile_pairs(q, kv, tile) + ms_per_q_tile * nq + ms_per_task;
+}
+
+double PlannerOptions::item_cost(const Item& it) const {
+  if (!cost.enabled) {
+    const int chunks = (it.head.len() > 0) + (it.tail.len() > 0);
+    return it.flops() + (chunks ? per_task_overhead_flops : 0.0);
+  }
+  return cost.chunk_ms(it.head.len(), it.head.b) + cost.chunk_ms(it.tail.len(), it.tail.b);
+}
+
+double PlannerOptions::marginal_cost(const Item& it) const {
+  // one token off the head's end and one off the tail's start: doc_len + 1 query-key pairs
+  if (!cost.enabled) return it.doc_len + 1.0;
+  const double t = (double)cost.tile;
+  return cost.ms_per_tile_pair * (it.doc_len + 1.0) / (t * t) + 2.0 * cost.ms_per_q_tile / t;
+}
+
 // ---------------------------------------------------------------------------------------------
 // linear layout
 // ---------------------------------------------------------------------------------------------
@@ -277,25 +309,35 @@ std::vector<Item> water_fill(const std::vector<Item>& layout, const PlannerOptio
 std::vector<Item> balance(const std::vector<Item>& items_in, const PlannerOptions& opt) {
   std::vector<Item> items = items_in;
   const int W = opt.world;
+  // Everything below is in the units of opt.item_cost(): predicted milliseconds with the cost model,
+  // query-key pairs without it.
   std::vector<double> load(W, 0.0);
   std::vector<double> item_flops(items.size());
   for (size_t i = 0; i < items.size(); ++i) {
-    item_flops[i] = items[i].flops() + opt.per_task_overhead_flops;
+    item_flops[i] = opt.item_cost(items[i]);
     load[items[i].dst] += item_flops[i];
   }
   const double total = std::accumulate(load.begin(), load.end(), 0.0);
   const double avg = total / W;
   const double threshold = avg * opt.tolerance;
+  // every server's target: an equal share, or a share in proportion to its measured speed
+  std::vector<double> target(W, avg);
+  if ((int)opt.speed.size() == W) {
+    double ssum = 0.0;
+    for (double v : opt.speed) ssum += v > 0 ? v : 0.0;
+    if (ssum > 0)
+      for (int r = 0; r < W; ++r) target[r] = total * (opt.speed[r] > 0 ? opt.speed[r] : 0.0) / ssum;
+  }
   std::vector<double> surplus(W);
-  for (int r = 0; r < W; ++r) surplus[r] = load[r] - avg;
+  for (int r = 0; r < W; ++r) surplus[r] = load[r] - target[r];
 
   std::vector<int> recipients;
   for (int r = 0; r < W; ++r)
     if (surplus[r] < 0) recipients.push_back(r);
   std::stable_sort(recipients.begin(), recipients.end(), [&](int a, int b) { return surplus[a] < surplus[b]; });
 
-  // One transfer of at most `need` FLOPs to `rcv`, taken from the cheapest (bytes per FLOP) item
-  // among the servers `donor_ok` admits. Returns the FLOPs moved (0 = nothing movable).
+  // One transfer of at most `need` cost units to `rcv`, taken from the cheapest (bytes per unit of cost)
+  // item among the servers `donor_ok` admits. Returns the cost moved (0 = nothing movable).
   auto transfer = [&](int rcv, double need, auto donor_ok) -> double {
     int best = -1;
     double best_prio = std::numeric_limits<double>::infinity();
@@ -306,7 +348,7 @@ std::vector<Item> balance(const std::vector<Item>& items_in, const PlannerOption
       if (d == rcv || surplus[d] <= 0 || item_flops[i] <= 0 || !donor_ok(d)) continue;
       const double movable = std::min({surplus[d], need, item_flops[i]});
       if (movable <= 0) continue;
-      const double q_tokens = movable / (it.doc_len + 1.0);
+      const double q_tokens = movable / opt.marginal_cost(it);
       const double bytes = q_tokens * opt.dims.q_row_bytes + 2.0 * (it.doc_len + 1.0) * opt.dims.kv_row_bytes;
       const double prio = bytes / movable;
       if (prio < best_prio) {
@@ -326,14 +368,15 @@ std::vector<Item> balance(const std::vector<Item>& items_in, const PlannerOption
     }
     Item& it = items[best];
     const int limit = it.whole() ? it.head.len() / 2 : std::min(it.head.len(), it.tail.len());
-    int m = (int)(best_max / (it.doc_len + 1.0));
+    int m = (int)(best_max / opt.marginal_cost(it));
+    if (opt.cost.enabled && m > opt.cost.tile) m = m / opt.cost.tile * opt.cost.tile;   // cut on tile boundaries
     if (m > limit) m = limit;
     if (m <= 0) return 0.0;
-    const double before = it.flops();
+    const double before = item_flops[best];
     const Item piece = cut_middle(it, m, rcv);
-    const double after = it.flops();
-    const double gained = piece.flops() + opt.per_task_overhead_flops;
-    item_flops[best] = after + opt.per_task_overhead_flops;
+    const double after = opt.item_cost(it);
+    const double gained = opt.item_cost(piece);
+    item_flops[best] = after;
     surplus[donor] -= (before - after);
     surplus[rcv] += gained;
     items.push_back(piece);  // invalidates `it`

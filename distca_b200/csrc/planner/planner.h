@@ -56,6 +56,24 @@ struct ModelDims {
   int kv_row_bytes = 2048;   // bytes of one token's K row (V is the same)
 };
 
+// Profiled cost of core attention (forward + backward) in milliseconds, tile-granular like the kernels:
+// a chunk of q queries whose last one sees kv keys costs
+//     ms_per_tile_pair * (128 x 128 query-key tile pairs the kernels visit, diagonal tiles counted whole)
+//   + ms_per_q_tile    * (128-row query tiles: pipeline fill, statistics, epilogue per tile)
+//   + ms_per_task      (once per chunk).
+// The constants come from the attention micro-benchmarks of this repository's kernels (see
+// distca_b200/planner/__init__.py::default_cost_model). With `enabled` false the balancer counts query-key
+// pairs, as the reference does (distca/planner/planner.py:366-378); its time model is a table over document
+// lengths used by its simulator only (distca/timemodule/compute.py:75-118).
+struct CostModel {
+  bool enabled = false;
+  int tile = 128;
+  double ms_per_tile_pair = 0.0;
+  double ms_per_q_tile = 0.0;
+  double ms_per_task = 0.0;
+  double chunk_ms(int q, int kv) const;
+};
+
 struct PlannerOptions {
   int world = 1;                 // attention-server ranks
   long tokens_per_rank = 0;      // capacity of the linear layout
@@ -63,7 +81,16 @@ struct PlannerOptions {
   ModelDims dims;
   long max_q_rows = 0;           // arena capacity per server in rows (0 = unlimited)
   long max_kv_rows = 0;
-  double per_task_overhead_flops = 0.0;  // time-model hook: fixed cost charged per chunk
+  double per_task_overhead_flops = 0.0;  // fixed cost charged per chunk when balancing by query-key pairs
+  CostModel cost;                        // balance predicted milliseconds instead of query-key pairs
+  // Relative speed of every server (empty = all equal): server r is given the share speed[r] / sum(speed) of
+  // the work. The runtime feeds back measured / predicted attention time here (GPUs under a power cap do
+  // not all run at the same clock).
+  std::vector<double> speed;
+  // cost of an item under these options: milliseconds (cost model) or query-key pairs
+  double item_cost(const Item& it) const;
+  // cost of moving one more token from the end of the head AND the start of the tail of `it`
+  double marginal_cost(const Item& it) const;
 };
 
 // One core-attention task on a server (rows are in the server's receive arena).
@@ -108,7 +135,9 @@ struct Plan {
   std::vector<Item> items;              // after balancing
   std::vector<RankPlan> ranks;
   std::vector<double> flops_before, flops_after;
-  double imbalance_before = 0.0, imbalance_after = 0.0;  // max / mean
+  double imbalance_before = 0.0, imbalance_after = 0.0;  // max / mean of query-key pairs
+  std::vector<double> cost_after;       // what the balancer balanced: predicted ms (cost model) or pairs, per server
+  double cost_imbalance_after = 0.0;    // max over servers of cost / (that server's share of the total)
   bool fits = true;                     // arena capacity respected
 };
 

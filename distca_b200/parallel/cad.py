@@ -44,7 +44,7 @@ import torch
 from ..models.config import ModelConfig, ParallelConfig, TrainConfig
 from ..ops import attention as attn_ops
 from ..ops import elementwise as ew
-from ..planner import Planner, PlannerConfig
+from ..planner import Planner, PlannerConfig, default_cost_model
 from ..utils import timers
 from .p2p import PeerArena, SignalBoard, scatter_rows, sum_slots
 
@@ -75,6 +75,17 @@ class CadRuntime:
         self.plan_stats: dict = {}
         self.last_plan = None
         self.capacity_hint = 0      # tokens per rank to size the arena for (nano-batches vary in size)
+        # time-model balancing: the planner balances predicted milliseconds (tile-granular cost of this
+        # repository's attention kernels) and gives every server a share in proportion to its measured speed
+        self.use_cost_model = bool(train_cfg.extra.get("cost_model", True))
+        self.speed_feedback = bool(train_cfg.extra.get("speed_feedback", True))
+        import threading
+        self._plan_lock = threading.Lock()
+        self._pending_speed = None
+        self.speed = None                   # relative speed per server after the last feedback
+        self._attn_events: list = []        # (start, end) CUDA events of this step's attention calls
+        self._predicted_ms = 0.0            # what the cost model predicted for them
+        self.predicted_ms = 0.0             # cost-model milliseconds (forward + backward) of the current plan on this server
 
     # ------------------------------------------------------------------------------------------
     def _setup(self, T: int) -> None:
@@ -109,7 +120,8 @@ class CadRuntime:
         self.SLOTS = a.view(self.off["SLOTS"], (self.C, T, 2 * self.kd), torch.bfloat16)
         self.planner = Planner(PlannerConfig(world=W, tokens_per_rank=T, tolerance=self.tolerance,
                                              q_row_bytes=self.q_bytes, kv_row_bytes=self.kv_bytes,
-                                             max_q_rows=self.max_q, max_kv_rows=self.max_kv))
+                                             max_q_rows=self.max_q, max_kv_rows=self.max_kv,
+                                             cost_model=default_cost_model(self.hq) if self.use_cost_model else None))
 
     # ------------------------------------------------------------------------------------------
     def make_plan(self, docs_per_rank: list[list[int]]):
@@ -119,11 +131,15 @@ class CadRuntime:
             self._setup(cap)
         assert cap <= self.T, "tokens per rank grew beyond the arena capacity"
         policy = self.tcfg.extra.get("attention_policy", "cad")
-        if policy == "cp":
-            return self.planner.plan_fixed_cp(docs_per_rank)   # baseline: per-document context parallelism
-        if policy == "water_fill":
-            return self.planner.plan_fixed_water_fill(docs_per_rank)   # legacy: only the longest document moves
-        return self.planner.plan_fixed(docs_per_rank)
+        with self._plan_lock:       # the planning thread and the step's thread never plan at the same time
+            if self._pending_speed is not None:
+                self.planner.set_speed(self._pending_speed)
+                self._pending_speed = None
+            if policy == "cp":
+                return self.planner.plan_fixed_cp(docs_per_rank)   # baseline: per-document context parallelism
+            if policy == "water_fill":
+                return self.planner.plan_fixed_water_fill(docs_per_rank)   # legacy: only the longest document moves
+            return self.planner.plan_fixed(docs_per_rank)
 
     def make_tables(self, plan) -> dict:
         """Host-only: this rank's address tables and attention work lists for ``plan`` as numpy arrays
@@ -171,7 +187,10 @@ class CadRuntime:
                                  + (int(orow0) + np.arange(n, dtype=np.int64)) * (2 * self.kv_bytes))
         t["kv_ret"] = kv_ret
         flops = np.asarray(plan.flops_after)
+        cost = np.asarray(plan.cost_after)
+        t["predicted_ms"] = float(cost[self.me]) if self.use_cost_model else 0.0
         t["stats"] = {"imbalance_before": plan.imbalance_before, "imbalance_after": plan.imbalance_after,
+                      "cost_imbalance_after": plan.cost_imbalance_after,
                       "tolerance": plan.tolerance_used, "q_rows": t["q_rows"], "kv_rows": t["kv_rows"],
                       "tasks": int(len(tasks)), "send_bytes": rp.send_bytes.tolist(),
                       "my_flops_share": float(flops[self.me] / max(flops.sum(), 1.0))}
@@ -185,7 +204,11 @@ class CadRuntime:
         if self.arena is None:
             self._setup(max(cap, self.capacity_hint))
         assert cap <= self.T, "tokens per rank grew beyond the arena capacity"
-        return self.planner.plan(batches)
+        with self._plan_lock:
+            if self._pending_speed is not None:
+                self.planner.set_speed(self._pending_speed)
+                self._pending_speed = None
+            return self.planner.plan(batches)
 
     def plan_step(self, docs_per_rank: list[list[int]], dp_rank: int | None = None, plan=None, tables=None) -> None:
         """Plan core attention for this slot's documents (``docs_per_rank[r]`` may be empty) and put
@@ -213,7 +236,55 @@ class CadRuntime:
         self.q_ret = torch.from_numpy(tables["q_ret"]).to(dev)
         self.kv_ret = torch.from_numpy(tables["kv_ret"]).to(dev)
         self.plan_stats = tables["stats"]
+        self.predicted_ms = tables.get("predicted_ms", 0.0)
 
+    # ------------------------------------------------------------------------------------------
+    # measured-speed feedback into the planner
+    _FWD_SHARE = 0.23      # forward share of the cost model's forward + backward milliseconds
+
+    def _timed_attention(self, share: float):
+        """Context manager: CUDA events around one attention call (read back at the end of the step)."""
+        rt = self
+
+        class _T:
+            def __enter__(self_inner):
+                if rt.speed_feedback and rt.use_cost_model:
+                    self_inner.a = torch.cuda.Event(enable_timing=True)
+                    self_inner.a.record()
+                return self_inner
+
+            def __exit__(self_inner, *exc):
+                if rt.speed_feedback and rt.use_cost_model:
+                    b = torch.cuda.Event(enable_timing=True)
+                    b.record()
+                    rt._attn_events.append((self_inner.a, b))
+                    rt._predicted_ms += rt.predicted_ms * share
+                return False
+        return _T()
+
+    def end_of_step_feedback(self, smoothing: float = 0.5) -> None:
+        """Collective over the attention group, called once per step after the device was synchronised:
+        every server reports measured / predicted attention time of the step; the planner's next plans give
+        server ``r`` work in proportion to its speed (GPUs under a power cap do not run at one clock, and the
+        cost model is not exact). The reference balances with fixed costs only."""
+        if not (self.speed_feedback and self.use_cost_model) or self.arena is None:
+            return
+        measured = sum(a.elapsed_time(b) for a, b in self._attn_events)
+        predicted, self._attn_events, self._predicted_ms = self._predicted_ms, [], 0.0
+        import torch.distributed as dist
+        mine = torch.tensor([measured, predicted], dtype=torch.float32, device=self.device)
+        allv = torch.empty(self.W, 2, dtype=torch.float32, device=self.device)
+        dist.all_gather_into_tensor(allv, mine, group=self.group)
+        allv = allv.cpu().numpy().astype(np.float64)
+        if (allv <= 0).any():
+            return                       # a server without work this step: keep the current speeds
+        speed = allv[:, 1] / allv[:, 0]          # predicted work per measured millisecond
+        speed = np.clip(speed / speed.mean(), 0.8, 1.25)
+        if self.speed is not None:
+            speed = smoothing * speed + (1.0 - smoothing) * self.speed
+        self.speed = speed / speed.mean()
+        self._pending_speed = self.speed.tolist()
+        self.plan_stats["speed"] = [round(float(v), 4) for v in self.speed]
     # ------------------------------------------------------------------------------------------
     # server halves (every rank of the group runs them once per layer and direction)
     def _serve_forward(self) -> None:
@@ -223,7 +294,7 @@ class CadRuntime:
     def _serve_forward_begin(self) -> None:
         with timers.phase("cad_wait_qkv"):
             self.sig.wait(SIG_QKV)
-        with timers.phase("cad_attn_fwd"):
+        with timers.phase("cad_attn_fwd"), self._timed_attention(self._FWD_SHARE):
             attn_ops.flash_fwd(self.Qr, self.Kr, self.Vr, self.attn_plan, out=self.AO.unflatten(1, (self.hq, self.D)),
                                lse=self.LSE, work_dev=self.fwd_work)
         self.sig.signal(SIG_OUT)
@@ -244,7 +315,7 @@ class CadRuntime:
         dq = torch.empty(nq, self.hq, self.D, dtype=torch.bfloat16, device=self.device)
         dk = torch.empty(nk, self.hkv, self.D, dtype=torch.bfloat16, device=self.device)
         dv = torch.empty(nk, self.hkv, self.D, dtype=torch.bfloat16, device=self.device)
-        with timers.phase("cad_attn_bwd"):
+        with timers.phase("cad_attn_bwd"), self._timed_attention(1.0 - self._FWD_SHARE):
             if self.q_rows:
                 attn_ops.flash_bwd(self.Qr[:nq], self.Kr[:nk], self.Vr[:nk], None, lse, self.dOr[:nq],
                                    self.attn_plan, dq=dq, dk=dk, dv=dv, scratch=self.scratch,

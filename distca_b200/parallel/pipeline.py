@@ -175,6 +175,8 @@ class PipelineTrainer:
         loss_sum /= self.par.tp
         self.step_idx += 1
         value = float(loss_sum.item())
+        if self.cad is not None and hasattr(self.cad, "end_of_step_feedback"):
+            self.cad.end_of_step_feedback()
         self.check_device_status()      # raises when a kernel of this step reported a failed wait / bounds check
         return value
 

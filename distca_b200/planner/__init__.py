@@ -42,6 +42,8 @@ class PlannerConfig:
     max_q_rows: int = 0              # arena capacity (rows) per server; 0 = unlimited
     max_kv_rows: int = 0
     per_task_overhead_flops: float = 0.0
+    cost_model: dict | None = None   # see default_cost_model(); None = balance query-key pairs like the reference
+    speed: list | None = None        # relative speed per server (None = equal shares)
 
     @staticmethod
     def for_model(cfg: ModelConfig, world: int, tokens_per_rank: int, tp: int = 1, elt: int = 2,
@@ -61,8 +63,24 @@ class Planner:
         o.dims = d
         o.max_q_rows, o.max_kv_rows = cfg.max_q_rows, cfg.max_kv_rows
         o.per_task_overhead_flops = cfg.per_task_overhead_flops
+        if cfg.cost_model:
+            c = self.ext.CostModel()
+            c.enabled = True
+            c.tile = int(cfg.cost_model.get("tile", 128))
+            c.ms_per_tile_pair = float(cfg.cost_model["ms_per_tile_pair"])
+            c.ms_per_q_tile = float(cfg.cost_model.get("ms_per_q_tile", 0.0))
+            c.ms_per_task = float(cfg.cost_model.get("ms_per_task", 0.0))
+            o.cost = c
+        if cfg.speed is not None:
+            o.speed = [float(v) for v in cfg.speed]
         self.options = o
         self.dims = d
+
+    def set_speed(self, speed) -> None:
+        """Relative speed of every attention server (``None`` = equal): the balancer gives server ``r`` the
+        share ``speed[r] / sum(speed)`` of the predicted attention time. Fed back by the runtime from the
+        measured time of earlier steps."""
+        self.options.speed = [] if speed is None else [float(v) for v in speed]
 
     def plan(self, docs_per_seq: list[list[int]], with_dummy: bool = False):
         """``docs_per_seq``: document lengths of every sequence of the batch, in rank order."""
@@ -124,14 +142,29 @@ class AsyncPlanner:
         self.pool.shutdown(wait=False, cancel_futures=True)
 
 
+def default_cost_model(heads_q: int = 32, kind: str = "b200") -> dict:
+    """Tile-granular cost of core attention, forward + backward, for the balancer (``PlannerConfig.cost_model``).
+
+    ``b200``: least-squares fit of ``ms = a * tile_pairs + b * query_tiles`` to this repository's kernels on one
+    B200 with 32 query / 8 KV heads of 128 (``kernel_bench --kernel attn_fwd / attn_bwd``: one document of 8192
+    tokens 0.535 + 1.732 ms, of 32768 tokens 7.24 + 25.59 ms, sixteen of 2048 tokens 0.664 + 2.035 ms), scaled
+    by the number of query heads on the rank. A query tile costs as much as 3.6 tile pairs, so a server full of
+    short documents is slower per query-key pair than one holding a single long document, which counting pairs
+    alone (the reference's balancer, distca/planner/planner.py:366-378) does not see."""
+    if kind != "b200":
+        raise ValueError(kind)
+    s = heads_q / 32.0
+    return {"tile": 128, "ms_per_tile_pair": 9.68e-4 * s, "ms_per_q_tile": 3.5e-3 * s, "ms_per_task": 0.0}
+
+
 def default_time_model(kind: str = "b200"):
     """Attention/linear cost tables. ``b200``: measured with this repository's kernels on one B200
     (whole causal document, 32 query / 8 KV heads of 128, forward); ``h100``: the reference's
     FlashAttention-2 profile (distca/profiling/data/compute-attn-H100.csv, 64/4 heads)."""
     tm = _ext().TimeModel()
     if kind == "b200":
-        tm.attn_len = [8192.0, 32768.0, 131072.0]
-        tm.attn_ms = [0.603, 7.532, 133.784]
+        tm.attn_len = [2048.0, 8192.0, 32768.0, 131072.0]
+        tm.attn_ms = [0.0415, 0.535, 7.24, 112.0]
         tm.linear_ms_per_token = 0.0
         tm.link_gbytes_per_s = 770.0
     elif kind == "h100":

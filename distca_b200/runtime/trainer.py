@@ -334,6 +334,9 @@ class Trainer:
             dist.all_reduce(loss, group=self.groups.dp_group)
         self.step_idx += 1
         value = float(loss.item())
+        for ca in self.core_attns:
+            if hasattr(ca, "end_of_step_feedback"):
+                ca.end_of_step_feedback()       # measured attention time of this step steers the next plans
         # the read above synchronised: a wait that ran out or a failed bounds check in this step raises here,
         # before the caller logs the loss, checkpoints or starts another step (the Adam kernels of such a
         # step have already skipped their update)

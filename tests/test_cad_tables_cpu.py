@@ -36,6 +36,8 @@ def _runtime(me, world, T, hq=4, hkv=2, D=128):
         cur += v + 16 * 1024
     rt.sizes = sizes
     rt.plan_stats, rt.last_plan = {}, None
+    import threading
+    rt.use_cost_model, rt.speed_feedback, rt._plan_lock, rt._pending_speed = False, False, threading.Lock(), None
     return rt
 
 

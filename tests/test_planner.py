@@ -181,3 +181,43 @@ def test_water_fill_policy_moves_only_the_longest_document():
     # two long documents: water filling cannot fix the second one, the balancer can
     docs2 = [[16 * K], [12 * K, 4 * K], [2 * K] * 8, [1 * K] * 16]
     assert p.plan_fixed(docs2).imbalance_after <= p.plan_fixed_water_fill(docs2).imbalance_after + 1e-9
+
+
+def test_cost_model_counts_the_tile_pairs_the_kernels_visit():
+    """``CostModel.chunk_ms`` with unit tile-pair cost against a direct count over 128-row query tiles."""
+    import numpy as np
+    from distca_b200.planner import Planner, PlannerConfig
+    cost = Planner(PlannerConfig(world=2, tokens_per_rank=1024, cost_model={"ms_per_tile_pair": 1.0})).options.cost
+    rng = np.random.default_rng(0)
+    for _ in range(500):
+        kv = int(rng.integers(1, 6000))
+        q = int(rng.integers(1, kv + 1))
+        want = sum((kv - q + min((i + 1) * 128, q) + 127) // 128 for i in range((q + 127) // 128))
+        assert cost.chunk_ms(q, kv) == want
+    assert cost.chunk_ms(0, 100) == 0.0
+
+
+def test_balancer_with_cost_model_and_server_speeds():
+    """Balancing predicted milliseconds: every server ends within the tolerance of ITS share, and a server
+    reported 10 % slower gets about 10 % less work."""
+    import numpy as np
+    from distca_b200.planner import Planner, PlannerConfig, default_cost_model
+    from distca_b200.data.synthetic import SyntheticBatches
+    cm = default_cost_model()
+    docs = SyntheticBatches(65536, 8, "mixture", 5, 32000).next_doc_lens()
+    even = Planner(PlannerConfig(world=8, tokens_per_rank=65536, tolerance=0.02, cost_model=cm)).plan_fixed(docs)
+    c = np.asarray(even.cost_after)
+    assert c.max() / c.mean() <= 1.03 and abs(even.cost_imbalance_after - c.max() / c.mean()) < 1e-9
+    speed = [1.0] * 7 + [0.9]
+    slow = Planner(PlannerConfig(world=8, tokens_per_rank=65536, tolerance=0.02, cost_model=cm, speed=speed)).plan_fixed(docs)
+    c = np.asarray(slow.cost_after)
+    share = c / c.sum()
+    want = np.asarray(speed) / sum(speed)
+    assert np.all(np.abs(share / want - 1.0) <= 0.035), share / want
+    assert slow.cost_imbalance_after <= 1.035
+    # every token is still placed exactly once
+    q = {}
+    for it in slow.items:
+        (ha, hb), (ta, tb) = it["head"], it["tail"]
+        q[it["doc"]] = q.get(it["doc"], 0) + hb - ha + tb - ta
+    assert sorted(q.values()) == sorted(L for d in docs for L in d)
