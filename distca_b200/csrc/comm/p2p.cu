@@ -157,6 +157,36 @@ reduce_scatter_sumsq_bf16_kernel(const unsigned long long* __restrict__ peer_bas
   }
 }
 
+// Same for fp32 gradient buffers (several micro-batches accumulate in fp32; the reference reduces its
+// gradients in fp32 as well, distca/utils/megatron_test_utils.py:237-241): 4 elements per thread and access.
+__global__ void __launch_bounds__(256)
+reduce_scatter_sumsq_f32_kernel(const unsigned long long* __restrict__ peer_base, int n_peers, int self,
+                                long lo_elems, long n, float* __restrict__ sumsq) {
+  __shared__ float sh[8];
+  const long nvec = n / 4;
+  float ss = 0.f;
+  float* own = reinterpret_cast<float*>(peer_base[self]) + lo_elems;
+  for (long i = blockIdx.x * (long)blockDim.x + threadIdx.x; i < nvec; i += (long)gridDim.x * blockDim.x) {
+    float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
+    for (int p = 0; p < n_peers; ++p) {
+      const float4 u = *reinterpret_cast<const float4*>(reinterpret_cast<const float*>(peer_base[p]) + lo_elems + i * 4);
+      acc.x += u.x; acc.y += u.y; acc.z += u.z; acc.w += u.w;
+    }
+    ss += acc.x * acc.x + acc.y * acc.y + acc.z * acc.z + acc.w * acc.w;
+    *reinterpret_cast<float4*>(own + i * 4) = acc;
+  }
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) ss += __shfl_xor_sync(0xffffffffu, ss, o);
+  if ((threadIdx.x & 31) == 0) sh[threadIdx.x >> 5] = ss;
+  __syncthreads();
+  if (threadIdx.x < 8) {
+    float t = sh[threadIdx.x];
+#pragma unroll
+    for (int o = 4; o > 0; o >>= 1) t += __shfl_xor_sync(0xffu, t, o);
+    if (threadIdx.x == 0) atomicAdd(sumsq, t);
+  }
+}
+
 // Parameter all-gather over peer memory: every rank pushes its shard into every peer's flat buffer.
 __global__ void __launch_bounds__(256)
 push_shard_kernel(const uint4* __restrict__ src, const unsigned long long* __restrict__ peer_base, int n_peers,
@@ -279,6 +309,19 @@ extern "C" int dca_reduce_scatter_sumsq_bf16(const void* peer_base, int n_peers,
   const long cap = (long)sm_count() * 8;
   if (blocks > cap) blocks = cap;
   p2p::reduce_scatter_sumsq_bf16_kernel<<<(int)blocks, 256, 0, (cudaStream_t)stream>>>(
+      (const unsigned long long*)peer_base, n_peers, self, lo_elems, n, sumsq);
+  DCA_CUDA_TRY(cudaGetLastError());
+  return 0;
+}
+// fp32 twin of dca_reduce_scatter_sumsq_bf16 (n and lo_elems multiples of 4).
+extern "C" int dca_reduce_scatter_sumsq_f32(const void* peer_base, int n_peers, int self, long lo_elems, long n,
+                                            float* sumsq, void* stream) {
+  if (n <= 0) return 0;
+  if (n % 4 != 0 || lo_elems % 4 != 0) return kErrBadArg;
+  long blocks = (n / 4 + 255) / 256;
+  const long cap = (long)sm_count() * 8;
+  if (blocks > cap) blocks = cap;
+  p2p::reduce_scatter_sumsq_f32_kernel<<<(int)blocks, 256, 0, (cudaStream_t)stream>>>(
       (const unsigned long long*)peer_base, n_peers, self, lo_elems, n, sumsq);
   DCA_CUDA_TRY(cudaGetLastError());
   return 0;

@@ -213,9 +213,10 @@ __global__ void adam_kernel(__nv_bfloat16* __restrict__ param, short* __restrict
 // all-gather: the updated bf16 parameters are stored into the flat parameter buffer of EVERY
 // data-parallel peer at element offset `lo` (peer_param[p] may be a peer mapping over NVLink), so no
 // separate collective is needed after the update. param/lo16/grad/m/v point at the shard itself.
+template <typename GradT>
 __global__ void __launch_bounds__(256)
 adam_push_kernel(const __nv_bfloat16* __restrict__ param, short* __restrict__ lo16,
-                 const __nv_bfloat16* __restrict__ grad, float* __restrict__ m, float* __restrict__ v, long n,
+                 const GradT* __restrict__ grad, float* __restrict__ m, float* __restrict__ v, long n,
                  float lr, float beta1, float beta2, float eps, float wd, float bc1, float bc2,
                  const float* __restrict__ gscale_ptr, const unsigned long long* __restrict__ peer_param,
                  int n_peers, long lo, const unsigned int* __restrict__ status) {
@@ -225,17 +226,24 @@ adam_push_kernel(const __nv_bfloat16* __restrict__ param, short* __restrict__ lo
   for (long i = blockIdx.x * (long)blockDim.x + threadIdx.x; i < nvec; i += (long)gridDim.x * blockDim.x) {
     const uint4 pu = *reinterpret_cast<const uint4*>(param + i * 8);
     const uint4 lu = *reinterpret_cast<const uint4*>(lo16 + i * 8);
-    const uint4 gu = *reinterpret_cast<const uint4*>(grad + i * 8);
+    float gq8[8];
+    if constexpr (sizeof(GradT) == 4) {
+      const float4 g0 = *reinterpret_cast<const float4*>(grad + i * 8), g1 = *reinterpret_cast<const float4*>(grad + i * 8 + 4);
+      gq8[0] = g0.x; gq8[1] = g0.y; gq8[2] = g0.z; gq8[3] = g0.w; gq8[4] = g1.x; gq8[5] = g1.y; gq8[6] = g1.z; gq8[7] = g1.w;
+    } else {
+      const uint4 gu = *reinterpret_cast<const uint4*>(grad + i * 8);
+      const float2 a = unpack_bf16x2(gu.x), b = unpack_bf16x2(gu.y), c = unpack_bf16x2(gu.z), d = unpack_bf16x2(gu.w);
+      gq8[0] = a.x; gq8[1] = a.y; gq8[2] = b.x; gq8[3] = b.y; gq8[4] = c.x; gq8[5] = c.y; gq8[6] = d.x; gq8[7] = d.y;
+    }
     float4 m0 = *reinterpret_cast<const float4*>(m + i * 8), m1 = *reinterpret_cast<const float4*>(m + i * 8 + 4);
     float4 v0 = *reinterpret_cast<const float4*>(v + i * 8), v1 = *reinterpret_cast<const float4*>(v + i * 8 + 4);
-    const uint32_t pw[4] = {pu.x, pu.y, pu.z, pu.w}, lw[4] = {lu.x, lu.y, lu.z, lu.w}, gw[4] = {gu.x, gu.y, gu.z, gu.w};
+    const uint32_t pw[4] = {pu.x, pu.y, pu.z, pu.w}, lw[4] = {lu.x, lu.y, lu.z, lu.w};
     float mm[8] = {m0.x, m0.y, m0.z, m0.w, m1.x, m1.y, m1.z, m1.w};
     float vv[8] = {v0.x, v0.y, v0.z, v0.w, v1.x, v1.y, v1.z, v1.w};
     uint32_t po[4], lo_out[4];
 #pragma unroll
     for (int j = 0; j < 4; ++j) {
-      const float2 gf = unpack_bf16x2(gw[j]);
-      const float gq[2] = {gf.x * gs, gf.y * gs};
+      const float gq[2] = {gq8[2 * j] * gs, gq8[2 * j + 1] * gs};
       uint32_t hi_out[2], rem_out[2];
 #pragma unroll
       for (int h = 0; h < 2; ++h) {
@@ -340,10 +348,10 @@ extern "C" int dca_sumsq(const void* g, int g_fp32, long n, float* sumsq, void* 
 
 // `status` (may be null): the device status word; when it is non-zero the update is skipped, so a step whose
 // kernels reported a failed wait or bounds check leaves the weights and the optimizer state as they were.
-// AdamW + parameter all-gather in one kernel (bf16 gradients). param/lo16/grad/m/v: this rank's
+// AdamW + parameter all-gather in one kernel (bf16 or fp32 gradients: g_fp32). param/lo16/grad/m/v: this rank's
 // shard (n elements, multiple of 8); peer_param: device array of n_peers addresses of the peers'
 // (and this rank's own) flat parameter buffers; lo: element offset of the shard in those buffers.
-extern "C" int dca_adam_push(const void* param, void* lo16, const void* grad, float* m, float* v, long n, float lr,
+extern "C" int dca_adam_push(const void* param, void* lo16, const void* grad, int g_fp32, float* m, float* v, long n, float lr,
                              float beta1, float beta2, float eps, float wd, int step, const float* gscale_ptr,
                              const void* peer_param, int n_peers, long lo, const unsigned int* status,
                              void* stream) {
@@ -351,9 +359,14 @@ extern "C" int dca_adam_push(const void* param, void* lo16, const void* grad, fl
   if (n % 8 != 0 || lo % 8 != 0) return kErrBadArg;
   const float bc1 = 1.f - powf(beta1, (float)step);
   const float bc2 = 1.f - powf(beta2, (float)step);
-  adam_push_kernel<<<grid_for(n / 8, 256), 256, 0, (cudaStream_t)stream>>>(
-      (const __nv_bfloat16*)param, (short*)lo16, (const __nv_bfloat16*)grad, m, v, n, lr, beta1, beta2, eps, wd, bc1,
-      bc2, gscale_ptr, (const unsigned long long*)peer_param, n_peers, lo, status);
+  if (g_fp32)
+    adam_push_kernel<float><<<grid_for(n / 8, 256), 256, 0, (cudaStream_t)stream>>>(
+        (const __nv_bfloat16*)param, (short*)lo16, (const float*)grad, m, v, n, lr, beta1, beta2, eps, wd, bc1,
+        bc2, gscale_ptr, (const unsigned long long*)peer_param, n_peers, lo, status);
+  else
+    adam_push_kernel<__nv_bfloat16><<<grid_for(n / 8, 256), 256, 0, (cudaStream_t)stream>>>(
+        (const __nv_bfloat16*)param, (short*)lo16, (const __nv_bfloat16*)grad, m, v, n, lr, beta1, beta2, eps, wd, bc1,
+        bc2, gscale_ptr, (const unsigned long long*)peer_param, n_peers, lo, status);
   DCA_CUDA_TRY(cudaGetLastError());
   return 0;
 }

@@ -20,16 +20,20 @@ from .p2p import PeerArena, SignalBoard
 
 
 class PeerDataParallel:
-    def __init__(self, group, device, numel: int):
+    def __init__(self, group, device, numel: int, grad_dtype=torch.bfloat16):
+        """``grad_dtype``: bf16 (one micro-batch per step: the weight-gradient GEMMs round once) or fp32
+        (several micro-batches accumulate; the reference's ``grad_reduce_in_fp32``)."""
         self.device = torch.device(device)
         nbytes = numel * 2
-        self.arena = PeerArena(2 * nbytes + (1 << 20), group, device)
+        gbytes = numel * (4 if grad_dtype == torch.float32 else 2)
+        self.grad_dtype = grad_dtype
+        self.arena = PeerArena(nbytes + gbytes + (1 << 20), group, device)
         self.size, self.rank = self.arena.size, self.arena.rank
         self.sig = SignalBoard(self.arena, 2)
         self.off_param = self.arena.alloc(nbytes, align=4096)
-        self.off_grad = self.arena.alloc(nbytes, align=4096)
+        self.off_grad = self.arena.alloc(gbytes, align=4096)
         self.flat = self.arena.view(self.off_param, (numel,), torch.bfloat16)
-        self.grad = self.arena.view(self.off_grad, (numel,), torch.bfloat16)
+        self.grad = self.arena.view(self.off_grad, (numel,), grad_dtype)
         self.param_tbl = torch.tensor([self.arena.addr(p, self.off_param) for p in range(self.size)],
                                       dtype=torch.int64, device=device)
         self.grad_tbl = torch.tensor([self.arena.addr(p, self.off_grad) for p in range(self.size)],
@@ -39,12 +43,15 @@ class PeerDataParallel:
         """own_grad[lo:lo+n] = sum over ranks; ``sumsq[0] += ||that||^2``. Collective over the group."""
         self.sig.signal(0)      # my backward is complete (stream order) ...
         self.sig.wait(0)        # ... and so is everybody else's
-        rc = _lib.lib().dca_reduce_scatter_sumsq_bf16(_lib.ptr(self.grad_tbl), _lib.c_int(self.size), _lib.c_int(self.rank),
-                                                      _lib.c_long(lo), _lib.c_long(n), _lib.ptr(sumsq), _lib.stream_ptr())
+        fn = (_lib.lib().dca_reduce_scatter_sumsq_f32 if self.grad_dtype == torch.float32
+              else _lib.lib().dca_reduce_scatter_sumsq_bf16)
+        rc = fn(_lib.ptr(self.grad_tbl), _lib.c_int(self.size), _lib.c_int(self.rank),
+                _lib.c_long(lo), _lib.c_long(n), _lib.ptr(sumsq), _lib.stream_ptr())
         _lib.check_rc(rc, "reduce_scatter_sumsq")
 
     def adam_push(self, pshard, lo16, gshard, m, v, lo: int, *, lr, beta1, beta2, eps, weight_decay, step, gscale) -> None:
-        rc = _lib.lib().dca_adam_push(_lib.ptr(pshard), _lib.ptr(lo16), _lib.ptr(gshard), _lib.ptr(m), _lib.ptr(v),
+        rc = _lib.lib().dca_adam_push(_lib.ptr(pshard), _lib.ptr(lo16), _lib.ptr(gshard),
+                                      _lib.c_int(1 if gshard.dtype == torch.float32 else 0), _lib.ptr(m), _lib.ptr(v),
                                       _lib.c_long(pshard.numel()), _lib.c_float(lr), _lib.c_float(beta1),
                                       _lib.c_float(beta2), _lib.c_float(eps), _lib.c_float(weight_decay), _lib.c_int(step),
                                       _lib.ptr(gscale), _lib.ptr(self.param_tbl), _lib.c_int(self.size), _lib.c_long(lo),

@@ -116,7 +116,7 @@ class ShardedAdam:
     def step(self) -> None:
         c = self.cfg
         self.step_count += 1
-        if self.p2p is not None and self.dp > 1 and self.store.grad.dtype == torch.bfloat16:
+        if self.p2p is not None and self.dp > 1:
             self._step_peer()
             return
         reduced = self.reduce_gradients()

@@ -1,20 +1,26 @@
 """Pipeline parallelism: a tick-synchronous 1F1B schedule whose idle slots serve attention.
 
-Tick ``t`` has a forward slot and a backward slot on EVERY stage:
+Stage ``p`` of ``pp`` runs the forward of micro-batch ``f - p`` in forward slot ``f`` and the backward of
+micro-batch ``b - (pp - 1 - p)`` in backward slot ``b`` (real if that index is in ``[0, M)``, else a dummy).
+There are ``M + pp - 1`` forward slots and as many backward slots, laid out as the reference does
+(distca/runtime/megatron/forward_backward_func.py:217-223, 279-300, 365-470):
 
-    forward  slot of stage p : micro-batch  t - p                  (real if 0 <= . < M, else dummy)
-    backward slot of stage p : micro-batch  t - 2(pp-1) + p        (real if 0 <= . < M, else dummy)
+    warm-up    pp - 1 ticks   forward slot only      (slots f = 0 .. pp-2)
+    steady     M ticks        forward + backward     (f = pp-1+i, b = i)
+    cool-down  pp - 1 ticks   backward slot only     (b = M .. M+pp-2)
 
-so the last stage runs the backward of a micro-batch in the tick of its forward, gradients reach
-stage p one tick per stage later, and there are ``M + 2(pp-1)`` ticks. With core-attention
-disaggregation every dp x pp rank is an attention server in every slot: a stage whose slot is a
-dummy owns no tokens there but still runs the attention tasks the planner gives it, layer by layer,
-in lock-step with the stages that do real work. Each slot has its own CAD plan over all ranks
-(forward slots: the documents each stage is running forward; backward slots likewise), which is
-the reference's per-tick planning (distca/utils/test_util.py:481-556, 582-795) with its
-dummy forward / dummy backward (distca/runtime/megatron/forward_backward_func.py:283-300, 365-380,
-427-470). Activations and activation gradients travel between stages with NCCL point-to-point
-(``batch_isend_irecv``), tensors of shape [tokens / tp, hidden].
+so the last stage runs the backward of a micro-batch in the tick of its forward, and a gradient reaches
+stage p one tick per stage later. With core-attention disaggregation every dp x pp rank is an attention
+server in every slot: a stage whose slot is a dummy owns no tokens there but still runs the attention tasks
+the planner gives it, layer by layer, in lock-step with the stages that do real work. Each slot has its own
+CAD plan over all ranks (the reference's per-tick planning, distca/utils/test_util.py:481-556, 582-795);
+all plans of a step (and of the next step, :meth:`PipelineTrainer.prefetch_plan`) are built on a planning
+thread while the GPU works.
+
+Activations and activation gradients travel between stages with NCCL point-to-point, tensors of shape
+[tokens / tp, hidden]: the exchange of a slot is started as soon as the slot's kernels are queued and is
+waited for only where the received tensor is consumed (the next tick), so the transfer overlaps the other
+slot's compute.
 """
 from __future__ import annotations
 
@@ -29,35 +35,66 @@ from .groups import build_groups
 from .optimizer import ShardedAdam
 
 
+def slot_schedule(M: int, pp: int) -> list[tuple[int | None, int | None]]:
+    """``(forward slot index or None, backward slot index or None)`` of every tick of a step:
+    ``pp - 1`` forward-only ticks, ``M`` ticks with both slots, ``pp - 1`` backward-only ticks."""
+    ticks = []
+    for t in range(M + 2 * (pp - 1)):
+        f = t if t < M + pp - 1 else None
+        b = t - (pp - 1) if t >= pp - 1 else None
+        ticks.append((f, b))
+    return ticks
+
+
 class PipelineTrainer:
     def __init__(self, model_cfg: ModelConfig, par: ParallelConfig, train_cfg: TrainConfig, *, num_microbatch: int,
                  device=None, seed: int = 0):
         assert par.pp > 1 and model_cfg.num_layers % par.pp == 0
         assert num_microbatch >= 1
+        # tied input / output embeddings live on different stages: their values and gradients would have to be
+        # kept equal across the first and the last stage, which this engine does not do
+        assert not model_cfg.tie_embeddings, "tie_embeddings is not supported with pipeline stages"
         self.model_cfg, self.par, self.cfg, self.M = model_cfg, par, train_cfg, num_microbatch
         self.rank, self.world = dist.get_rank(), dist.get_world_size()
         assert self.world == par.world
         if device is None:
             device = torch.device("cuda", torch.cuda.current_device()) if torch.cuda.is_available() else torch.device("cpu")
         self.device = torch.device(device)
+        on_gpu = self.device.type == "cuda"
         self.tp_rank, self.dp_rank, self.pp_rank = par.coords(self.rank)
         self.groups = build_groups(par, self.rank)
         tp = None
         if par.tp > 1:
             from .tensor_parallel import TensorParallel
-            tp = TensorParallel(self.groups.tp_group, par.tp, self.tp_rank, self.device)
+            # default on GPUs: all-gather / reduce-scatter fused into the GEMMs over peer memory
+            tp = TensorParallel(self.groups.tp_group, par.tp, self.tp_rank, self.device,
+                                use_p2p=train_cfg.extra.get("tp_transport", "p2p") == "p2p",
+                                max_cols=model_cfg.hidden)
         per = model_cfg.num_layers // par.pp
         self.first, self.last = self.pp_rank == 0, self.pp_rank == par.pp - 1
         grad_dtype = {"bf16": None, "fp32": torch.float32}[train_cfg.grad_dtype]
-        if num_microbatch > 1 and grad_dtype is None and self.device.type == "cuda":
+        if num_microbatch > 1 and grad_dtype is None and on_gpu:
             grad_dtype = torch.float32  # several micro-batches accumulate into the gradient buffer
+        self.p2p = None
+        buffers = None
+        if par.dp > 1 and on_gpu and train_cfg.extra.get("dp_transport", "p2p") == "p2p":
+            # parameters and gradients in peer-mapped memory: reduce-scatter and parameter all-gather run in
+            # this repository's kernels over NVLink (fp32 gradients when micro-batches accumulate)
+            from .dp_p2p import PeerDataParallel
+
+            def buffers(numel):
+                self.p2p = PeerDataParallel(self.groups.dp_group, self.device, numel,
+                                            grad_dtype=grad_dtype or torch.bfloat16)
+                return self.p2p.flat, self.p2p.grad
         self.model = LlamaModel(model_cfg, self.device, tp=tp, layer_range=(self.pp_rank * per, (self.pp_rank + 1) * per),
                                 first_stage=self.first, last_stage=self.last, grad_dtype=grad_dtype, seed=seed,
                                 recompute=train_cfg.recompute, lm_head_chunk=train_cfg.lm_head_chunk,
-                                pad_params_to=par.dp)
+                                pad_params_to=par.dp, param_buffers=buffers)
+        for layer in self.model.layers:
+            layer.fuse_rope = bool(train_cfg.extra.get("fuse_qkv_rope", True))
         self.local_attn = LocalCoreAttention(model_cfg, par.tp)
         self.cad = None
-        if train_cfg.cad and par.dp * par.pp > 1 and self.device.type == "cuda":
+        if train_cfg.cad and par.dp * par.pp > 1 and on_gpu:
             from .cad import CadRuntime
             self.cad = CadRuntime(model_cfg, par, train_cfg, self.groups, self.device,
                                   tolerance=float(train_cfg.extra.get("tolerance", 0.1)))
@@ -68,46 +105,85 @@ class PipelineTrainer:
         repl = tuple(n for n, _ in self.model.store.shapes if n.endswith("norm_weight") or n.endswith("layernorm.weight"))
         self.opt = ShardedAdam(self.model.store, train_cfg, dp_group=self.groups.dp_group if par.dp > 1 else None,
                                norm_group=self.groups.world_group, replicated_names=repl if par.tp > 1 else (),
-                               tp_rank=self.tp_rank)
+                               tp_rank=self.tp_rank, p2p=self.p2p)
         self.prev = par.rank_of(self.tp_rank, self.dp_rank, self.pp_rank - 1) if not self.first else None
         self.next = par.rank_of(self.tp_rank, self.dp_rank, self.pp_rank + 1) if not self.last else None
         self.act_dtype = self.model.dtype
         self.step_idx = 0
         from ..utils.watchdog import StepGuard
         self.guard = StepGuard.for_process_group()     # heartbeat check before, watchdog around every step
+        self._plan_pool = None
+        self._plans_ahead = None         # (document table of the step, {(which, slot): Future})
+        self.last_schedule = None        # what the last step ran: ticks, slots, bubble fraction
 
     # ------------------------------------------------------------------------------------------
-    def _exchange(self, send_next=None, send_prev=None, recv_prev_shape=None, recv_next_shape=None):
-        ops, rp, rn = [], None, None
-        if send_next is not None:
-            ops.append(dist.P2POp(dist.isend, send_next.contiguous(), self.next))
-        if send_prev is not None:
-            ops.append(dist.P2POp(dist.isend, send_prev.contiguous(), self.prev))
-        if recv_prev_shape is not None:
-            rp = torch.empty(recv_prev_shape, dtype=self.act_dtype, device=self.device)
-            ops.append(dist.P2POp(dist.irecv, rp, self.prev))
-        if recv_next_shape is not None:
-            rn = torch.empty(recv_next_shape, dtype=self.act_dtype, device=self.device)
-            ops.append(dist.P2POp(dist.irecv, rn, self.next))
-        if ops:
-            for w in dist.batch_isend_irecv(ops):
-                w.wait()
-        return rp, rn
+    # stage-to-stage exchange: started when the slot's kernels are queued, waited for where consumed
+    def _start_exchange(self, send: torch.Tensor | None, send_to, recv_shape, recv_from):
+        ops, recv = [], None
+        if send is not None:
+            ops.append(dist.P2POp(dist.isend, send.contiguous(), send_to))
+        if recv_shape is not None:
+            recv = torch.empty(recv_shape, dtype=self.act_dtype, device=self.device)
+            ops.append(dist.P2POp(dist.irecv, recv, recv_from))
+        works = dist.batch_isend_irecv(ops) if ops else []
+        return works, recv, send      # the sent tensor is kept alive until the exchange was waited for
 
-    def _slot_docs(self, all_mb_docs, which: str, tick: int):
+    @staticmethod
+    def _finish_exchange(pending):
+        if pending is None:
+            return None
+        works, recv, _sent = pending
+        for w in works:
+            w.wait()
+        return recv
+
+    # ------------------------------------------------------------------------------------------
+    # per-slot core-attention plans
+    def _slot_docs(self, all_mb_docs, which: str, slot: int):
         """Documents every rank of the attention group owns in a slot, in attention-group rank order
         (pp-major, dp-minor: the order build_groups uses)."""
-        pp, dp = self.par.pp, self.par.dp
+        pp, dp, M = self.par.pp, self.par.dp, len(all_mb_docs)
         out = []
         for p in range(pp):
-            mb = tick - p if which == "fwd" else tick - 2 * (pp - 1) + p
+            mb = slot - p if which == "fwd" else slot - (pp - 1 - p)
             for d in range(dp):
-                out.append(list(all_mb_docs[mb][d]) if 0 <= mb < self.M else [])
+                out.append(list(all_mb_docs[mb][d]) if 0 <= mb < M else [])
         return out
 
-    def _set_attention(self, all_mb_docs, which, tick, mb):
+    def _submit_plans(self, all_mb_docs) -> dict:
+        """Queue the host work (C++ plan + address tables) of every slot of a step on the planning thread, in
+        the order the slots run. The first plan of a run sizes the arena, which is a collective: it is made
+        by the caller, synchronously, before this is used."""
+        if self._plan_pool is None:
+            from concurrent.futures import ThreadPoolExecutor
+            self._plan_pool = ThreadPoolExecutor(max_workers=1, thread_name_prefix="cad-planner")
+        futs = {}
+
+        def work(docs, cad=self.cad):
+            plan = cad.make_plan(docs)
+            return plan, (cad.make_tables(plan) if plan.fits else None)
+        for f, b in slot_schedule(len(all_mb_docs), self.par.pp):
+            for which, slot in (("fwd", f), ("bwd", b)):
+                if slot is not None:
+                    futs[(which, slot)] = self._plan_pool.submit(work, self._slot_docs(all_mb_docs, which, slot))
+        return futs
+
+    def prefetch_plan(self, hb_next) -> None:
+        """Plan every slot of the NEXT step on the planning thread while the current step runs."""
+        if self.cad is None or not hasattr(self.cad, "make_tables") or getattr(self.cad, "arena", None) is None:
+            return
+        _, all_mb_docs = self._microbatch_docs(hb_next)
+        self._plans_ahead = (all_mb_docs, self._submit_plans(all_mb_docs))
+
+    def _set_attention(self, all_mb_docs, plans, which, slot, mb):
         if self.cad is not None:
-            self.cad.plan_step(self._slot_docs(all_mb_docs, which, tick))
+            docs = self._slot_docs(all_mb_docs, which, slot)
+            fut = plans.get((which, slot)) if plans else None
+            if fut is not None:
+                plan, tables = fut.result()
+                self.cad.plan_step(docs, plan=plan, tables=tables)
+            else:
+                self.cad.plan_step(docs)
             return self.cad
         if 0 <= mb < self.M:
             self.local_attn.set_batch(AttnPlan(AttnTasks.from_doc_lens(all_mb_docs[mb][self.dp_rank]), self.device))
@@ -123,53 +199,88 @@ class PipelineTrainer:
             return self._train_step(hb)
 
     def _train_step(self, hb) -> float:
+        from ..utils import timers
+        from ..utils.observability import nvtx_range
         M, pp, p = self.M, self.par.pp, self.pp_rank
         self.model.store.zero_grad()
         T, all_mb_docs, batches = self._split_microbatches(hb)
+        if self.par.tp > 1:
+            self.model.tp.ensure_fused(T // self.par.tp)
         Tl = T // self.par.tp
         H = self.model_cfg.hidden
+        plans = None
+        if self.cad is not None and hasattr(self.cad, "make_tables"):
+            if self._plans_ahead is not None and self._plans_ahead[0] == all_mb_docs:
+                plans = self._plans_ahead[1]
+            elif getattr(self.cad, "arena", None) is not None:
+                plans = self._submit_plans(all_mb_docs)
+            self._plans_ahead = None
         saved = {}
         loss_sum = torch.zeros((), dtype=torch.float32, device=self.device)
-        x_in, dy_in = None, None
         n_layers = len(self.model.layers)
-        for tick in range(M + 2 * (pp - 1)):
-            f_mb = tick - p
-            b_mb = tick - 2 * (pp - 1) + p
+        pend_x = pend_dy = None           # exchanges in flight: next forward input / next backward gradient
+        ticks = slot_schedule(M, pp)
+        real = 0
+        for tick, (f, b) in enumerate(ticks):
             # ---------------- forward slot ----------------
-            ca = self._set_attention(all_mb_docs, "fwd", tick, f_mb)
-            x_out = None
-            if 0 <= f_mb < M:
-                x_out, saved[f_mb] = self.model.stage_forward(batches[f_mb], ca, x_in,
-                                                              keep_last=self.last and self.cad is None)
-            elif self.cad is not None:
-                for _ in range(n_layers):
-                    self.cad.dummy_forward()
+            if f is not None:
+                f_mb = f - p
+                with nvtx_range(f"tick{tick}.fwd.mb{f_mb if 0 <= f_mb < M else 'dummy'}"):
+                    x_in = self._finish_exchange(pend_x)
+                    pend_x = None
+                    ca = self._set_attention(all_mb_docs, plans, "fwd", f, f_mb)
+                    if plans is None and self.cad is not None and hasattr(self.cad, "make_tables") and tick == 0:
+                        plans = self._submit_plans(all_mb_docs)      # the arena exists now: plan the rest ahead
+                        plans.pop(("fwd", f), None)
+                    x_out = None
+                    if 0 <= f_mb < M:
+                        real += 1
+                        x_out, saved[f_mb] = self.model.stage_forward(batches[f_mb], ca, x_in,
+                                                                      keep_last=self.last and self.cad is None)
+                    elif self.cad is not None:
+                        for _ in range(n_layers):
+                            self.cad.dummy_forward()
+                    nf = f_mb + 1          # what this stage runs in its next forward slot
+                    more = f + 1 < M + pp - 1
+                    pend_x = self._start_exchange(
+                        x_out if (x_out is not None and not self.last) else None, self.next,
+                        (Tl, H) if (more and not self.first and 0 <= nf < M) else None, self.prev)
             # ---------------- backward slot ----------------
-            ca = self._set_attention(all_mb_docs, "bwd", tick, b_mb)
-            dx = None
-            if 0 <= b_mb < M:
-                loss, dx = self.model.stage_backward(batches[b_mb], ca, saved.pop(b_mb), dy_in)
-                if loss is not None:
-                    loss_sum += loss
-            elif self.cad is not None:
-                for li in range(n_layers):
-                    if self.model.recompute == "keep_attn":
-                        # the recompute half only re-dispatches Q/K/V (nothing to send from here), no attention runs
-                        self.cad.no_tokens_dispatch()
-                        self.cad.restore_no_tokens(li)
-                    else:
-                        self.cad.dummy_forward()    # the recompute half of a backward slot
-                    self.cad.dummy_backward()
-            # ---------------- hand activations / gradients to the neighbours ----------------
-            nf, nb = f_mb + 1, b_mb + 1       # what this stage runs in the next tick
-            x_in, dy_in = self._exchange(
-                send_next=x_out if (x_out is not None and not self.last) else None,
-                send_prev=dx if (dx is not None and not self.first) else None,
-                recv_prev_shape=(Tl, H) if (not self.first and 0 <= nf < M) else None,
-                recv_next_shape=(Tl, H) if (not self.last and 0 <= nb < M) else None)
+            if b is not None:
+                b_mb = b - (pp - 1 - p)
+                with nvtx_range(f"tick{tick}.bwd.mb{b_mb if 0 <= b_mb < M else 'dummy'}"):
+                    dy_in = self._finish_exchange(pend_dy)
+                    pend_dy = None
+                    ca = self._set_attention(all_mb_docs, plans, "bwd", b, b_mb)
+                    dx = None
+                    if 0 <= b_mb < M:
+                        real += 1
+                        loss, dx = self.model.stage_backward(batches[b_mb], ca, saved.pop(b_mb), dy_in)
+                        if loss is not None:
+                            loss_sum += loss
+                    elif self.cad is not None:
+                        for li in range(n_layers):
+                            if self.model.recompute == "keep_attn":
+                                # the recompute half only re-dispatches Q/K/V (nothing to send from here), no attention runs
+                                self.cad.no_tokens_dispatch()
+                                self.cad.restore_no_tokens(li)
+                            else:
+                                self.cad.dummy_forward()    # the recompute half of a backward slot
+                            self.cad.dummy_backward()
+                    nb = b_mb + 1
+                    more = b + 1 < M + pp - 1
+                    pend_dy = self._start_exchange(
+                        dx if (dx is not None and not self.first) else None, self.prev,
+                        (Tl, H) if (more and not self.last and 0 <= nb < M) else None, self.next)
+        self._finish_exchange(pend_x)
+        self._finish_exchange(pend_dy)
+        slots = 2 * (M + pp - 1)
+        self.last_schedule = {"ticks": len(ticks), "forward_slots": M + pp - 1, "backward_slots": M + pp - 1,
+                              "real_slots_this_stage": real, "bubble_fraction": 1.0 - real / slots}
         if self.par.tp > 1:
             self.model.tp.sync_replicated_grads(self.model.store)
-        self.opt.step()
+        with timers.phase("optimizer"):
+            self.opt.step()
         # the loss lives on the last stage: share it with everybody (sum over dp, max trick over pp)
         dist.all_reduce(loss_sum, group=self.groups.world_group)
         loss_sum /= self.par.tp
@@ -180,10 +291,10 @@ class PipelineTrainer:
         self.check_device_status()      # raises when a kernel of this step reported a failed wait / bounds check
         return value
 
-    def _split_microbatches(self, hb):
+    def _microbatch_docs(self, hb):
+        """(tokens per micro-batch, documents [micro-batch][dp rank]) of a host batch."""
         M = self.M
         T = hb.ids.numel() // M
-        self.model.ensure_positions(max(hb.doc_lens, default=0))
         all_mb_docs = [[[] for _ in range(self.par.dp)] for _ in range(M)]
         for d, docs in enumerate(hb.all_doc_lens):
             acc, mb = 0, 0
@@ -192,6 +303,12 @@ class PipelineTrainer:
                 acc += L
                 if acc == T:
                     acc, mb = 0, mb + 1
+        return T, all_mb_docs
+
+    def _split_microbatches(self, hb):
+        self.model.ensure_positions(max(hb.doc_lens, default=0))
+        T, all_mb_docs = self._microbatch_docs(hb)
+        M = self.M
         ids, labels, pos = (t.to(self.device, non_blocking=True) for t in (hb.ids, hb.labels, hb.pos))
         batches = [Batch(ids[i * T:(i + 1) * T], labels[i * T:(i + 1) * T], pos[i * T:(i + 1) * T], hb.num_valid_global)
                    for i in range(M)]
@@ -211,7 +328,7 @@ class PipelineTrainer:
             for tick in range(M + pp - 1):
                 f_mb = tick - p
                 # the plan of a forward slot covers the micro-batches every stage runs in this tick
-                ca = self._set_attention(all_mb_docs, "fwd", tick, f_mb)
+                ca = self._set_attention(all_mb_docs, None, "fwd", tick, f_mb)
                 x_out = None
                 if 0 <= f_mb < M:
                     x_out, _ = self.model.stage_forward(batches[f_mb], ca, x_in)
@@ -223,8 +340,9 @@ class PipelineTrainer:
                     for _ in range(n_layers):
                         self.cad.dummy_forward()
                 nf = f_mb + 1
-                x_in, _ = self._exchange(send_next=x_out if (x_out is not None and not self.last) else None,
-                                         recv_prev_shape=(Tl, H) if (not self.first and 0 <= nf < M) else None)
+                x_in = self._finish_exchange(self._start_exchange(
+                    x_out if (x_out is not None and not self.last) else None, self.next,
+                    (Tl, H) if (not self.first and 0 <= nf < M) else None, self.prev))
         finally:
             self.model.recompute = keep_policy
         dist.all_reduce(loss_sum, group=self.groups.world_group)
@@ -236,7 +354,19 @@ class PipelineTrainer:
             _lib.check_status(self.device, "pipeline step")
 
     def close(self) -> None:
+        """Release peer-mapped arenas (collective: every rank of the groups must call it)."""
+        if self._plan_pool is not None:
+            self._plan_pool.shutdown(wait=True)
+            self._plan_pool = None
         self.guard.close()
         if self.cad is not None:
             self.cad.close()
             self.cad = None
+        if self.par.tp > 1 and getattr(self.model.tp, "fused", None) is not None:
+            self.model.tp.fused.close()
+            self.model.tp.fused = None
+        if self.p2p is not None:
+            self.model = None
+            self.opt = None
+            self.p2p.close()
+            self.p2p = None

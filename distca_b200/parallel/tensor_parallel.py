@@ -24,9 +24,23 @@ class TensorParallel:
         self.device = torch.device(device)
         self.on_gpu = self.device.type == "cuda"
         self.fused = None   # PeerCollectives: all-gather / reduce-scatter fused into the GEMMs
-        if use_p2p and self.on_gpu and max_rows_local > 0:
-            from .tp_p2p import PeerCollectives
-            self.fused = PeerCollectives(group, size, rank, device, max_rows_local, max_cols)
+        self.use_p2p = use_p2p and self.on_gpu
+        self._max_cols = max_cols
+        if self.use_p2p and max_rows_local > 0:
+            self.ensure_fused(max_rows_local)
+
+    def ensure_fused(self, rows_local: int) -> None:
+        """Create (or grow) the peer arena of the fused collectives for ``rows_local`` tokens per rank.
+        Collective over the group; every rank calls it with the same value (the trainers do, at the first
+        step and whenever the micro-batch grows)."""
+        if not self.use_p2p:
+            return
+        if self.fused is not None and self.fused.max_rows >= rows_local:
+            return
+        if self.fused is not None:
+            self.fused.close()
+        from .tp_p2p import PeerCollectives
+        self.fused = PeerCollectives(self.group, self.size, self.rank, self.device, rows_local, self._max_cols)
 
     def all_gather_rows(self, x: torch.Tensor) -> torch.Tensor:
         out = torch.empty((x.shape[0] * self.size,) + tuple(x.shape[1:]), dtype=x.dtype, device=x.device)

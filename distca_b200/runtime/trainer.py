@@ -155,22 +155,25 @@ class Trainer:
         tp = None
         if par.tp > 1:
             from ..parallel.tensor_parallel import TensorParallel
+            # default on GPUs: all-gather / reduce-scatter fused into the GEMMs over peer memory
+            # (--tp-transport nccl keeps the NCCL collectives); the arena is sized at the first step
             tp = TensorParallel(self.groups.tp_group, par.tp, self.tp_rank, self.device,
-                                use_p2p=train_cfg.extra.get("tp_transport", "nccl") == "p2p",
+                                use_p2p=train_cfg.extra.get("tp_transport", "p2p") == "p2p",
                                 max_rows_local=int(train_cfg.extra.get("tp_max_rows_local", 0)),
                                 max_cols=max(model_cfg.hidden, 0))
         grad_dtype = {"bf16": None, "fp32": torch.float32}[train_cfg.grad_dtype]
         assert par.pp == 1, "pipeline stages are built by parallel.pipeline.PipelineTrainer"
         self.p2p = None
         buffers = None
-        if (par.dp > 1 and self.device.type == "cuda" and grad_dtype is None
+        if (par.dp > 1 and self.device.type == "cuda"
                 and train_cfg.extra.get("dp_transport", "p2p") == "p2p"):
             # parameters and gradients live in peer-mapped memory so that the gradient reduce-scatter
             # and the parameter all-gather run inside our own kernels over NVLink
             from ..parallel.dp_p2p import PeerDataParallel
 
             def buffers(numel):
-                self.p2p = PeerDataParallel(self.groups.dp_group, self.device, numel)
+                self.p2p = PeerDataParallel(self.groups.dp_group, self.device, numel,
+                                            grad_dtype=grad_dtype or torch.bfloat16)
                 return self.p2p.flat, self.p2p.grad
         self.model = LlamaModel(model_cfg, self.device, tp=tp, grad_dtype=grad_dtype, seed=seed,
                                 recompute=train_cfg.recompute, lm_head_chunk=train_cfg.lm_head_chunk,
@@ -299,6 +302,8 @@ class Trainer:
         with timers.phase("zero_grad"):
             self.model.store.zero_grad()
         self.model.ensure_positions(max(hb.doc_lens, default=0))
+        if self.par.tp > 1 and not isinstance(hb, SpanHostBatch):
+            self.model.tp.ensure_fused(hb.ids.numel() // self.par.tp)
         if isinstance(hb, SpanHostBatch):
             # documents may span ranks: the planner decides the layout, then this rank cuts out its tokens
             assert self.cad is not None and self.nano == 1, "spanning documents need core-attention disaggregation"
@@ -348,6 +353,8 @@ class Trainer:
         device tensor (no host synchronisation). Used for device-only timing."""
         self.model.store.zero_grad()
         self.model.ensure_positions(max(hb.doc_lens, default=0))
+        if self.par.tp > 1:
+            self.model.tp.ensure_fused(hb.ids.numel() // self.par.tp)
         if self.nano == 2:
             loss, _ = self.model.forward_backward_nano(batch, self.core_attns)   # batch: list of nano-batches
         else:
@@ -360,6 +367,8 @@ class Trainer:
 
     def eval_step(self, hb: HostBatch) -> float:
         self.model.ensure_positions(max(hb.doc_lens, default=0))
+        if self.par.tp > 1:
+            self.model.tp.ensure_fused(hb.ids.numel() // self.par.tp)
         batch = self.to_device(hb)
         self.plan_attention(hb)
         loss = self.model.forward_loss(batch, self.core_attn)
@@ -381,6 +390,9 @@ class Trainer:
             for ca in self.core_attns:
                 ca.close()
             self.cad = None
+        if self.par.tp > 1 and getattr(self.model.tp, "fused", None) is not None:
+            self.model.tp.fused.close()
+            self.model.tp.fused = None
         if self.p2p is not None:
             self.model = None
             self.opt = None

@@ -194,3 +194,34 @@ def test_prefetched_local_attention_plan_gives_the_same_step():
         out.append((l0, l1, tr.model.store.flat.clone()))
         tr.close()
     assert out[0][0] == out[1][0] and out[0][1] == out[1][1] and torch.equal(out[0][2], out[1][2])
+
+
+def test_pipeline_schedule_has_standard_1f1b_depth():
+    """``M + pp - 1`` forward slots and as many backward slots: ``pp - 1`` forward-only warm-up ticks, ``M``
+    steady ticks, ``pp - 1`` backward-only cool-down ticks (the reference's schedule,
+    distca/runtime/megatron/forward_backward_func.py:217-223, 279-300, 365-470); every stage runs every
+    micro-batch once forward and once backward, the backward never before the forward, and a gradient is
+    produced by stage p+1 strictly before stage p consumes it."""
+    from distca_b200.parallel.pipeline import slot_schedule
+    for pp in (2, 3, 4):
+        for M in (pp, pp + 1, 8):
+            ticks = slot_schedule(M, pp)
+            assert len(ticks) == M + 2 * (pp - 1)
+            fwd = [f for f, _ in ticks if f is not None]
+            bwd = [b for _, b in ticks if b is not None]
+            assert fwd == list(range(M + pp - 1)) and bwd == list(range(M + pp - 1))
+            assert all(b is None for _, b in ticks[:pp - 1]) and all(f is None for f, _ in ticks[-(pp - 1):])
+            when_f, when_b = {}, {}
+            for t, (f, b) in enumerate(ticks):
+                for p in range(pp):
+                    if f is not None and 0 <= f - p < M:
+                        when_f[(p, f - p)] = t
+                    if b is not None and 0 <= b - (pp - 1 - p) < M:
+                        when_b[(p, b - (pp - 1 - p))] = t
+            assert len(when_f) == len(when_b) == pp * M
+            for (p, mb), t in when_b.items():
+                assert t >= when_f[(p, mb)]
+                if p + 1 < pp:
+                    assert when_b[(p + 1, mb)] == t - 1 and when_f[(p + 1, mb)] == when_f[(p, mb)] + 1
+            # bubble: each stage is busy in 2M of its 2(M + pp - 1) slots
+            assert abs((1 - 2 * M / (2 * (M + pp - 1))) - (pp - 1) / (M + pp - 1)) < 1e-12
