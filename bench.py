@@ -39,6 +39,20 @@ os.environ.setdefault("NCCL_NVLS_ENABLE", "0")
 sys.path.insert(0, os.path.dirname(os.path.abspath(__file__)))
 
 
+# The fixed layouts of the contract's other configurations (8 GPUs each).
+NAMED_CONFIGS = {
+    "tp8_64k": {"what": "Llama-3-8B, TP=8, 8 packed sequences of 64K tokens per step, documents log-uniform [128, 65536]",
+                "model": "llama3-8b", "tp": 8, "pp": 1, "dp": 1, "seq_len": 65536, "seqs_per_rank": 8, "microbatches": 1,
+                "dist": "loguniform", "recompute": "keep_attn"},
+    "4d_128k": {"what": "Llama-3-8B, TP=2 x PP=2 x DP=2 with CAD, 128K-token sequences, long/short mixture",
+                "model": "llama3-8b", "tp": 2, "pp": 2, "dp": 2, "seq_len": 131072, "seqs_per_rank": 1, "microbatches": 2,
+                "dist": "mixture", "recompute": "keep_attn"},
+    "34b_256k": {"what": "CodeLlama-34B shape, TP=4 x PP=2 with CAD, 256K-token sequences, full activation recompute",
+                 "model": "codellama-34b", "tp": 4, "pp": 2, "dp": 1, "seq_len": 262144, "seqs_per_rank": 1, "microbatches": 2,
+                 "dist": "mixture", "recompute": "full"},
+}
+
+
 def _args():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
@@ -46,7 +60,7 @@ def _args():
     ap.add_argument("--warmup", type=int, default=3)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--model", default="llama3-8b")
-    ap.add_argument("--seq-len", type=int, default=131072)
+    ap.add_argument("--seq-len", type=int, default=None, help="tokens per packed sequence (headline: 131072; --config: its own)")
     ap.add_argument("--num-layers", type=int, default=None, help="debug only; the headline uses all layers")
     ap.add_argument("--dist", default="mixture")
     ap.add_argument("--no-cad", action="store_true")
@@ -58,9 +72,16 @@ def _args():
                     help="2: ping-pong schedule over two nano-batches per rank")
     ap.add_argument("--no-fuse-qkv-rope", action="store_true",
                     help="separate RoPE / dispatch kernel instead of the QKV GEMM epilogue (for A/B timing)")
+    ap.add_argument("--config", default="headline", choices=["headline", *NAMED_CONFIGS],
+                    help="headline: the dp{N} + CAD scaling benchmark (default); the others are fixed 8-GPU layouts: "
+                         + "; ".join(f"{k}: {v['what']}" for k, v in NAMED_CONFIGS.items()))
+    ap.add_argument("--baseline-mode", default="none", choices=["none", "percp"],
+                    help="percp (with --config): the no-CAD per-document context-parallel baseline on the same documents "
+                         "(tensor parallel x context parallel over the remaining ranks, all-gather K/V)")
+    ap.add_argument("--microbatches", type=int, default=None, help="micro-batches per step of a pipelined --config")
     ap.add_argument("--phase-timers", action="store_true",
                     help="CUDA-event phase timers in the device-timed region; the JSON line gains phases_ms_per_step")
-    ap.add_argument("--recompute", default="keep_attn", choices=["full", "keep_attn"],
+    ap.add_argument("--recompute", default=None, choices=["full", "keep_attn"],
                     help="keep_attn: recompute every layer in backward except core attention, whose output is kept "
                          "(HBM or pinned host memory); falls back to full when neither has room")
     return ap.parse_args()
@@ -139,10 +160,153 @@ class ClockSampler:
         return out
 
 
+def run_named_config(a) -> None:
+    """One of the fixed 8-GPU layouts (``--config``): every step goes through the public ``train_step`` call
+    (pinned host batch in, loss out); timed with CUDA events around each step and with the wall clock around
+    all of them, maximum over ranks. ``--baseline-mode percp`` runs the per-document context-parallel baseline
+    on the same global batches instead (TP unchanged, the other ranks form one context-parallel group)."""
+    import torch
+    import torch.distributed as dist
+    from distca_b200.models.config import ParallelConfig, TrainConfig, get_model_config
+    from distca_b200.runtime.trainer import BatchSource, Trainer, init_distributed
+    from distca_b200.utils import timers
+
+    spec = dict(NAMED_CONFIGS[a.config])
+    rank, world, local = init_distributed()
+    tp, pp, dp = spec["tp"], spec["pp"], spec["dp"]
+    M = a.microbatches or spec["microbatches"]
+    seq_len = a.seq_len or spec["seq_len"]
+    percp = a.baseline_mode == "percp"
+    seqs_per_step = dp * spec["seqs_per_rank"] * (M if pp > 1 else 1)
+    if percp:
+        # same global batch; pipeline and data-parallel ranks become one context-parallel group
+        dp, pp = dp * pp, 1
+    assert world == tp * pp * dp, f"--config {a.config} needs {tp * pp * dp} GPUs, WORLD_SIZE={world}"
+    cfg = get_model_config(spec["model"], a.num_layers)
+    par = ParallelConfig(tp=tp, pp=pp, dp=dp)
+    recompute = a.recompute or spec["recompute"]
+    tc = TrainConfig(cad=not (a.no_cad or percp), recompute=recompute, comm_buffer_gb=a.comm_buffer_gb)
+    tc.extra.update(tolerance=a.tolerance, attention_policy=a.attention_policy, fuse_qkv_rope=not a.no_fuse_qkv_rope,
+                    baseline_mode=a.baseline_mode)
+    if pp > 1:
+        from distca_b200.parallel.pipeline import PipelineTrainer
+        trainer = PipelineTrainer(cfg, par, tc, num_microbatch=M, seed=0)
+        seqs_per_rank = M * spec["seqs_per_rank"]
+    else:
+        trainer = Trainer(cfg, par, tc, seed=0)
+        seqs_per_rank = seqs_per_step // dp
+    dev = trainer.device
+
+    def source(seed):
+        if percp:
+            # one stream of seqs_per_step sequences; every rank takes the whole batch and cuts its chunks
+            return BatchSource(cfg, ParallelConfig(tp=1, pp=1, dp=seqs_per_step), seq_len, spec["dist"], seed=seed)
+        return BatchSource(cfg, par, seq_len, spec["dist"], seed=seed, seqs_per_rank=seqs_per_rank)
+
+    def draw(src):
+        return src.next_global() if percp else src.next(trainer.dp_rank)
+
+    def barrier():
+        torch.cuda.synchronize(dev)
+        dist.barrier()
+        torch.cuda.synchronize(dev)
+
+    warm_src, src = source(99), source(1234)
+    losses = [trainer.train_step(draw(warm_src)) for _ in range(a.warmup)]
+    batches = [draw(src) for _ in range(a.steps)]
+    sampler = ClockSampler(local) if rank == 0 else None
+    from distca_b200.ops import _lib
+    torch.cuda.reset_peak_memory_stats(dev)
+    barrier()
+    timers.enable(True)
+    launches0 = _lib.LAUNCHES
+    events = []
+    t0 = time.perf_counter()
+    for i, hb in enumerate(batches):
+        if i + 1 < len(batches) and hasattr(trainer, "prefetch_plan") and not percp:
+            trainer.prefetch_plan(batches[i + 1])
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        losses.append(trainer.train_step(hb))
+        e1.record()
+        events.append((e0, e1))
+    barrier()
+    ms_e2e = (time.perf_counter() - t0) * 1e3
+    ms_dev = sum(x.elapsed_time(y) for x, y in events)
+    launches = _lib.LAUNCHES - launches0
+    phases = timers.GLOBAL.summary()
+    timers.enable(False)
+    clocks = sampler.stop() if sampler is not None else None
+    exposed = sum(v for k, v in phases.items() if k.startswith("cad_wait") or k in ("cad_dispatch", "cad_return")) / a.steps
+    attn_ms = (phases.get("cad_attn_fwd", 0.0) + phases.get("cad_attn_bwd", 0.0) + phases.get("attn_fwd", 0.0) * 0
+               ) / a.steps
+    free, total_mem = torch.cuda.mem_get_info(dev)
+    t = torch.tensor([ms_dev, ms_e2e, exposed, attn_ms, (total_mem - free) / 2**30], dtype=torch.float64, device=dev)
+    tsum = torch.tensor([attn_ms], dtype=torch.float64, device=dev)
+    dist.all_reduce(t, op=dist.ReduceOp.MAX)
+    dist.all_reduce(tsum, op=dist.ReduceOp.SUM)
+    ms_dev, ms_e2e, exposed, attn_max, mem_gb = (float(x) for x in t)
+    attn_mean = float(tsum[0]) / world
+    tokens = seq_len * seqs_per_step * a.steps
+    if percp:
+        docs_of = lambda hb: [hb.doc_lens]
+        h2d = batches[0].tokens.numel() // dp * 20
+    else:
+        docs_of = lambda hb: hb.all_doc_lens
+        h2d = batches[0].nbytes()
+    lin_flop = 3.0 * cfg.flops_per_token_linear() * tokens
+    attn_flop = sum(3.0 * 2.0 * float(L) * L * cfg.head_dim * cfg.heads_q * cfg.num_layers
+                    for hb in batches for docs in docs_of(hb) for L in docs)
+    if rank == 0:
+        cad_rt = getattr(trainer, "cad", None)
+        out = {
+            "metric": f"{cfg.name}_{a.config}_tokens_per_sec_box", "value": tokens / (ms_dev / 1e3), "unit": "tokens/s",
+            "n_gpus": world, "steps": a.steps, "warmup": a.warmup, "ms_per_step": ms_dev / a.steps,
+            "higher_is_better": True, "scaling": "fixed 8-GPU layout", "vs_baseline": None, "dtype": "bf16",
+            "data": f"synthetic packed documents ({spec['dist']}), random-init weights",
+            "config": {"model": cfg.name, "layers": cfg.num_layers, "global_batch": seqs_per_step, "seq_len": seq_len,
+                       "parallelism": f"tp{tp}-" + (f"cp{dp}-percp" if percp else f"pp{pp}-dp{dp}" + ("-cad" if cad_rt is not None else "")),
+                       "microbatches": M if pp > 1 else 1, "recompute": recompute,
+                       "grad_dtype": str(trainer.model.store.grad.dtype).replace("torch.", ""),
+                       "tp_transport": "p2p" if (tp > 1 and getattr(trainer.model.tp, "use_p2p", False)) else ("nccl" if tp > 1 else None),
+                       "dp_transport": "p2p" if getattr(trainer, "p2p", None) is not None else ("nccl" if dp > 1 else None),
+                       "l2": "working set of every kernel exceeds L2 (inputs larger than L2)"},
+            "e2e": {"value": tokens / (ms_e2e / 1e3), "unit": "tokens/s", "ms_per_step": ms_e2e / a.steps,
+                    "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": 4},
+            "gpu_launches": launches,
+            "model_flops": {"linear_pflop_per_step": lin_flop / a.steps / 1e15,
+                            "attention_pflop_per_step": attn_flop / a.steps / 1e15,
+                            "achieved_pflops_per_gpu": (lin_flop + attn_flop) / (ms_dev / 1e3) / 1e15 / world},
+            "memory_gb_max_over_ranks": mem_gb, "clocks": clocks, "loss_first_last": [losses[0], losses[-1]],
+            "impl": "ours",
+        }
+        if getattr(trainer, "last_schedule", None):
+            out["pipeline"] = trainer.last_schedule
+        if cad_rt is not None:
+            out["cad"] = {"planned_imbalance_after": cad_rt.plan_stats.get("imbalance_after"),
+                          "planned_cost_imbalance_after": cad_rt.plan_stats.get("cost_imbalance_after"),
+                          "server_speed": cad_rt.plan_stats.get("speed"),
+                          "exposed_dispatch_ms_per_step": exposed,
+                          "attention_ms_per_step_max_over_ranks": attn_max,
+                          "attention_time_imbalance_max_over_mean": (attn_max / attn_mean) if attn_mean > 0 else None,
+                          "tolerance": a.tolerance}
+        if percp:
+            out["percp"] = {"kv_bytes_received_per_layer_and_rank": trainer.percp.bytes_per_layer}
+        if a.phase_timers:
+            out["phases_ms_per_step"] = {k: round(v / a.steps, 2) for k, v in sorted(phases.items())}
+        print(json.dumps(out))
+    trainer.close()
+    dist.barrier()
+    dist.destroy_process_group()
+
+
 def main() -> None:
     a = _args()
     if a.impl == "reference":
         reference_arm(a)
+        return
+    if a.config != "headline":
+        run_named_config(a)
         return
     import torch
     import torch.distributed as dist
@@ -152,6 +316,8 @@ def main() -> None:
 
     rank, world, local = init_distributed()
     assert world == a.gpus, f"--gpus {a.gpus} but WORLD_SIZE={world}"
+    a.seq_len = a.seq_len or 131072
+    a.recompute = a.recompute or "keep_attn"
     cfg = get_model_config(a.model, a.num_layers)
     par = ParallelConfig(tp=1, pp=1, dp=world)
     tc = TrainConfig(cad=not a.no_cad, recompute=a.recompute, comm_buffer_gb=a.comm_buffer_gb)
@@ -252,7 +418,9 @@ def main() -> None:
             "dtype": "bf16", "data": "synthetic packed documents (mixture of log-uniform lengths), random-init weights",
             "config": {"model": cfg.name, "layers": cfg.num_layers, "global_batch": world, "seq_len": a.seq_len,
                        "parallelism": (f"dp{world}-{a.attention_policy}" if trainer.cad is not None else f"dp{world}"),
-                       "recompute": trainer.model.recompute, "nano_batches": a.nano_batches, "attention_outputs_kept_in": store_where, "optimizer": "sharded AdamW, fp32 master weights (bf16 + 16-bit remainder)",
+                       "recompute": trainer.model.recompute, "nano_batches": a.nano_batches,
+                       "grad_dtype": str(trainer.model.store.grad.dtype).replace("torch.", ""),
+                       "dp_transport": "p2p" if trainer.p2p is not None else ("nccl" if world > 1 else None), "attention_outputs_kept_in": store_where, "optimizer": "sharded AdamW, fp32 master weights (bf16 + 16-bit remainder)",
                        "l2": "working set of every kernel exceeds L2 (inputs larger than L2)"},
             "e2e": {"value": e2e, "unit": "tokens/s", "ms_per_step": ms_e2e / a.steps,
                     "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": 4,
@@ -271,6 +439,8 @@ def main() -> None:
         if trainer.cad is not None:
             out["cad"] = {"planned_imbalance_after": trainer.cad.plan_stats.get("imbalance_after"),
                           "planned_imbalance_before": trainer.cad.plan_stats.get("imbalance_before"),
+                          "planned_cost_imbalance_after": trainer.cad.plan_stats.get("cost_imbalance_after"),
+                          "server_speed": trainer.cad.plan_stats.get("speed"),
                           "exposed_dispatch_ms_per_step": exposed,
                           "attention_ms_per_step_max_over_ranks": attn_max,
                           "attention_time_imbalance_max_over_mean": (attn_max / attn_mean) if attn_mean > 0 else None,

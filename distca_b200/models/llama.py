@@ -698,8 +698,9 @@ class LlamaModel:
         for i, layer in enumerate(self.layers):
             keep = self.recompute == "none" or i == nl - 1
             inputs.append(x)
-            x, ctx = layer.forward(x, batch.pos, self.rope_table, core_attn, keep,
-                                   attn_store=store if store is not None and store.has(layer.index) else None)
+            with timers.layer("fwd", layer.index):
+                x, ctx = layer.forward(x, batch.pos, self.rope_table, core_attn, keep,
+                                       attn_store=store if store is not None and store.has(layer.index) else None)
             ctxs.append(ctx)
         with timers.phase("lm_head"):
             loss, dx = self.head_loss_and_grad(x, batch.labels, batch.num_valid_global)
@@ -715,10 +716,12 @@ class LlamaModel:
                 if store is not None and store.has(layer.index):
                     saved = store.load(layer.index)
                     store.prefetch(self.layers[i - 1].index if i > 0 else -1)
-                _, ctx = layer.forward(inputs[i], batch.pos, self.rope_table, core_attn, True, saved_attn=saved)
+                with timers.layer("recompute", layer.index):
+                    _, ctx = layer.forward(inputs[i], batch.pos, self.rope_table, core_attn, True, saved_attn=saved)
                 del saved
             inputs[i] = None
-            dx = layer.backward(ctx, dx, batch.pos, self.rope_table, core_attn)
+            with timers.layer("bwd", layer.index):
+                dx = layer.backward(ctx, dx, batch.pos, self.rope_table, core_attn)
             del ctx
         with timers.phase("embed_bwd"):
             self.embed_bwd(batch.ids, dx)
@@ -741,7 +744,8 @@ class LlamaModel:
             keep = self.recompute == "none" or i == nl - 1
             inputs.append(xs)
             use = stores if stores is not None and stores[0].has(layer.index) else None
-            outs = layer.forward_nano(xs, poss, self.rope_table, cas, keep, stores=use)
+            with timers.layer("fwd", layer.index):
+                outs = layer.forward_nano(xs, poss, self.rope_table, cas, keep, stores=use)
             xs = [o[0] for o in outs]
             ctxs.append([o[1] for o in outs] if keep else None)
         loss = torch.zeros((), dtype=torch.float32, device=self.device)
@@ -764,11 +768,13 @@ class LlamaModel:
                         for k, st in enumerate(stores):
                             if inputs[i][k] is not None:
                                 st.prefetch(self.layers[i - 1].index)
-                outs = layer.forward_nano(inputs[i], poss, self.rope_table, cas, True, saved=saved)
+                with timers.layer("recompute", layer.index):
+                    outs = layer.forward_nano(inputs[i], poss, self.rope_table, cas, True, saved=saved)
                 cs = [o[1] for o in outs]
                 del saved, outs
             inputs[i] = None
-            dxs = layer.backward_nano(cs, dxs, poss, self.rope_table, cas)
+            with timers.layer("bwd", layer.index):
+                dxs = layer.backward_nano(cs, dxs, poss, self.rope_table, cas)
             del cs
         with timers.phase("embed_bwd"):
             for k in range(n):
@@ -805,7 +811,8 @@ class LlamaModel:
         for i, layer in enumerate(self.layers):
             keep = self.recompute == "none" or (keep_last and i == nl - 1)
             inputs.append(x)
-            x, ctx = layer.forward(x, batch.pos, self.rope_table, core_attn, keep, attn_store=store)
+            with timers.layer("fwd", layer.index):
+                x, ctx = layer.forward(x, batch.pos, self.rope_table, core_attn, keep, attn_store=store)
             ctxs.append(ctx)
         return x, (inputs, ctxs, x if self.last_stage else None, store)
 
@@ -825,10 +832,12 @@ class LlamaModel:
             ctx = ctxs[i]
             ctxs[i] = None
             if ctx is None:
-                _, ctx = layer.forward(inputs[i], batch.pos, self.rope_table, core_attn, True,
-                                       saved_attn=store.load(layer.index) if store is not None else None)
+                with timers.layer("recompute", layer.index):
+                    _, ctx = layer.forward(inputs[i], batch.pos, self.rope_table, core_attn, True,
+                                           saved_attn=store.load(layer.index) if store is not None else None)
             inputs[i] = None
-            dx = layer.backward(ctx, dx, batch.pos, self.rope_table, core_attn)
+            with timers.layer("bwd", layer.index):
+                dx = layer.backward(ctx, dx, batch.pos, self.rope_table, core_attn)
             del ctx
         if self.first_stage:
             with timers.phase("embed_bwd"):

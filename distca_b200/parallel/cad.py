@@ -278,6 +278,7 @@ class CadRuntime:
         allv = allv.cpu().numpy().astype(np.float64)
         if (allv <= 0).any():
             return                       # a server without work this step: keep the current speeds
+        self.last_measured = allv
         speed = allv[:, 1] / allv[:, 0]          # predicted work per measured millisecond
         speed = np.clip(speed / speed.mean(), 0.8, 1.25)
         if self.speed is not None:
@@ -285,6 +286,8 @@ class CadRuntime:
         self.speed = speed / speed.mean()
         self._pending_speed = self.speed.tolist()
         self.plan_stats["speed"] = [round(float(v), 4) for v in self.speed]
+        self.plan_stats["attention_ms_per_server"] = [round(float(v), 2) for v in allv[:, 0]]
+        self.plan_stats["attention_time_imbalance"] = float(allv[:, 0].max() / allv[:, 0].mean())
     # ------------------------------------------------------------------------------------------
     # server halves (every rank of the group runs them once per layer and direction)
     def _serve_forward(self) -> None:

@@ -24,6 +24,10 @@ from ..models.config import ParallelConfig, TrainConfig, get_model_config
 from .trainer import BatchSource, Trainer, init_distributed
 
 
+LOSS_RTOL = 2e-3        # relative difference of a step's loss between the two paths
+TENSOR_RTOL = 2e-2      # largest element-wise difference of a named gradient, relative to that tensor's largest entry
+
+
 def check_cad(a) -> int:
     rank, world, _ = init_distributed()
     cfg = get_model_config(a.model, a.layers)
@@ -48,6 +52,7 @@ def check_cad(a) -> int:
         tr.check_device_status()
         results[mode] = losses
         grads[mode] = tr.model.store.grad.float().clone()
+        offsets = dict(tr.model.store.offsets)
         if mode == "cad":
             results["plan"] = {k: v for k, v in tr.cad.plan_stats.items() if k != "send_bytes"}
         tr.close()
@@ -57,13 +62,23 @@ def check_cad(a) -> int:
     err = (g0 - g1).abs().max().item()
     scale = g0.abs().max().item() + 1e-12
     cos = torch.nn.functional.cosine_similarity(g0, g1, dim=0).item()
-    ok = all(abs(x - y) <= 2e-2 * abs(x) for x, y in zip(results["local"], results["cad"])) and cos > 0.995
+    # every named tensor on its own scale (the reference asserts rtol = atol = 1.1e-3 on one named gradient,
+    # tests/test_megatron_e2e_pipeline.py:414; bf16 kernels with different summation orders need a little more)
+    worst_name, worst_rel = None, 0.0
+    for name, (o, n) in offsets.items():
+        a0, a1 = g0[o:o + n], g1[o:o + n]
+        rel = (a0 - a1).abs().max().item() / (a0.abs().max().item() + 1e-12)
+        if rel > worst_rel:
+            worst_name, worst_rel = name, rel
+    ok = (all(abs(x - y) <= LOSS_RTOL * abs(x) for x, y in zip(results["local"], results["cad"]))
+          and worst_rel <= TENSOR_RTOL and cos > 0.9995)
     flags = torch.tensor([1 if ok else 0], device="cuda")
     dist.all_reduce(flags, op=dist.ReduceOp.MIN)
     if rank == 0:
         print(json.dumps({"check": "cad", "ok": bool(flags.item()), "parallel": par.describe(),
                           "loss_local": results["local"], "loss_cad": results["cad"], "grad_max_err": err,
-                          "grad_scale": scale, "grad_cosine": cos, "plan": results.get("plan")}))
+                          "grad_scale": scale, "grad_cosine": cos, "worst_tensor": worst_name,
+                          "worst_tensor_rel_err": worst_rel, "plan": results.get("plan")}))
     dist.barrier()
     return 0 if flags.item() else 1
 
@@ -88,12 +103,46 @@ def check_dp(a) -> int:
         torch.cuda.empty_cache()
     p0, p1 = out["nccl"][1], out["p2p"][1]
     err = (p0 - p1).abs().max().item()
-    ok = err <= 2e-2 * p0.abs().max().item() and all(abs(x - y) <= 2e-2 * abs(x) for x, y in zip(out["nccl"][0], out["p2p"][0]))
+    ok = err <= TENSOR_RTOL * p0.abs().max().item() and all(abs(x - y) <= LOSS_RTOL * abs(x) for x, y in zip(out["nccl"][0], out["p2p"][0]))
     flags = torch.tensor([1 if ok else 0], device="cuda")
     dist.all_reduce(flags, op=dist.ReduceOp.MIN)
     if rank == 0:
         print(json.dumps({"check": "dp", "ok": bool(flags.item()), "loss_nccl": out["nccl"][0], "loss_p2p": out["p2p"][0],
                           "param_max_diff": err, "grad_norm": [out["nccl"][2], out["p2p"][2]]}))
+    dist.barrier()
+    return 0 if flags.item() else 1
+
+
+def check_percp(a) -> int:
+    """The per-document context-parallel baseline (all-gather K/V, NCCL) against core-attention
+    disaggregation on the same global batches: different token layouts, same model, so the losses of a few
+    optimizer steps and the weights they produce must agree to bf16 accuracy."""
+    rank, world, _ = init_distributed()
+    cfg = get_model_config(a.model, a.layers)
+    par = ParallelConfig(tp=1, pp=1, dp=world)
+    out = {}
+    for mode in ("cad", "percp"):
+        tc = TrainConfig(cad=(mode == "cad"), recompute=a.recompute, lr=1e-3)
+        tc.extra["baseline_mode"] = "percp" if mode == "percp" else "none"
+        tr = Trainer(cfg, par, tc, seed=1)
+        src = BatchSource(cfg, par, a.tokens, a.dist, seed=a.seed)
+        losses = []
+        for _ in range(a.steps):
+            losses.append(tr.train_step(src.next_global() if mode == "percp" else src.next(tr.dp_rank)))
+        tr.check_device_status()
+        out[mode] = (losses, tr.model.store.flat.float().clone())
+        tr.close()
+        del tr
+        torch.cuda.empty_cache()
+    p0, p1 = out["cad"][1], out["percp"][1]
+    err = (p0 - p1).abs().max().item()
+    ok = (err <= TENSOR_RTOL * p0.abs().max().item()
+          and all(abs(x - y) <= LOSS_RTOL * abs(x) for x, y in zip(out["cad"][0], out["percp"][0])))
+    flags = torch.tensor([1 if ok else 0], device="cuda")
+    dist.all_reduce(flags, op=dist.ReduceOp.MIN)
+    if rank == 0:
+        print(json.dumps({"check": "percp", "ok": bool(flags.item()), "loss_cad": out["cad"][0],
+                          "loss_percp": out["percp"][0], "param_max_diff": err}))
     dist.barrier()
     return 0 if flags.item() else 1
 
@@ -121,7 +170,7 @@ def check_tp(a) -> int:
         torch.cuda.empty_cache()
     g0, g1 = out["nccl"][1], out["p2p"][1]
     cos = torch.nn.functional.cosine_similarity(g0, g1, dim=0).item()
-    ok = cos > 0.995 and all(abs(x - y) <= 2e-2 * abs(x) for x, y in zip(out["nccl"][0], out["p2p"][0]))
+    ok = cos > 0.9995 and all(abs(x - y) <= LOSS_RTOL * abs(x) for x, y in zip(out["nccl"][0], out["p2p"][0]))
     flags = torch.tensor([1 if ok else 0], device="cuda")
     dist.all_reduce(flags, op=dist.ReduceOp.MIN)
     if rank == 0:
@@ -133,7 +182,7 @@ def check_tp(a) -> int:
 
 def main() -> None:
     ap = argparse.ArgumentParser()
-    ap.add_argument("check", choices=["cad", "dp", "tp"])
+    ap.add_argument("check", choices=["cad", "dp", "tp", "percp"])
     ap.add_argument("--model", default="small-128")
     ap.add_argument("--layers", type=int, default=None)
     ap.add_argument("--tokens", type=int, default=8192)
@@ -147,7 +196,7 @@ def main() -> None:
     ap.add_argument("--recompute", default="full", choices=["full", "keep_attn"],
                     help="activation policy of the CAD run (the local run always recomputes fully)")
     a = ap.parse_args()
-    rc = {"cad": check_cad, "dp": check_dp, "tp": check_tp}[a.check](a)
+    rc = {"cad": check_cad, "dp": check_dp, "tp": check_tp, "percp": check_percp}[a.check](a)
     if dist.is_initialized():
         dist.destroy_process_group()
     sys.exit(rc)

@@ -194,6 +194,14 @@ class Trainer:
             self.cad = GlooCadRuntime(model_cfg, self.groups.attn_group, self.groups.attn_ranks, par.tp,
                                       tolerance=float(train_cfg.extra.get("tolerance", 0.1)), dtype=self.model.dtype)
             self.core_attn = self.cad
+        # baseline: per-document context parallelism over the same ranks, no disaggregation (all-gather K/V)
+        self.percp = None
+        if train_cfg.extra.get("baseline_mode", "none") == "percp" and par.dp * par.pp > 1:
+            assert self.cad is None and par.pp == 1, "--baseline-mode percp replaces CAD and has no pipeline stages"
+            from ..parallel.percp import PerDocCPAttention
+            self.percp = PerDocCPAttention(model_cfg, self.groups.attn_group, len(self.groups.attn_ranks),
+                                           self.groups.attn_ranks.index(self.rank), self.device, par.tp)
+            self.core_attn = self.percp
         # ping-pong: a second core-attention module (own arena, own plan) for the second nano-batch
         self.nano = int(train_cfg.extra.get("nano_batches", 1))
         assert self.nano in (1, 2)
@@ -302,8 +310,22 @@ class Trainer:
         with timers.phase("zero_grad"):
             self.model.store.zero_grad()
         self.model.ensure_positions(max(hb.doc_lens, default=0))
+        assert self.percp is None or isinstance(hb, SpanHostBatch), \
+            "the per-document CP baseline takes the global batch (BatchSource.next_global)"
         if self.par.tp > 1 and not isinstance(hb, SpanHostBatch):
             self.model.tp.ensure_fused(hb.ids.numel() // self.par.tp)
+        if isinstance(hb, SpanHostBatch) and self.percp is not None:
+            # baseline: every rank holds a head and a tail chunk of every document of the global batch
+            from ..parallel.percp import percp_layout
+            W = self.percp.W
+            with timers.phase("plan"):
+                ids, labels, pos = hb.materialise(percp_layout(hb.doc_lens, W, self.percp.me),
+                                                  int(hb.tokens.numel()) // W, pinned=self.device.type == "cuda")
+                self.percp.set_batch(hb.doc_lens)
+            batch = Batch(ids.to(self.device, non_blocking=True), labels.to(self.device, non_blocking=True),
+                          pos.to(self.device, non_blocking=True), hb.num_valid_global)
+            loss, _ = self.model.forward_backward(batch, self.core_attn)
+            return self._finish_step(loss)
         if isinstance(hb, SpanHostBatch):
             # documents may span ranks: the planner decides the layout, then this rank cuts out its tokens
             assert self.cad is not None and self.nano == 1, "spanning documents need core-attention disaggregation"
@@ -416,6 +438,13 @@ class BatchSource:
         self.stream = stream or SyntheticBatches(tokens_per_seq, par.dp * seqs_per_rank, dist_name, seed, model_cfg.vocab)
         self.seqs_per_rank = seqs_per_rank
         self.pinned = pinned and torch.cuda.is_available()
+
+    def next_global(self) -> SpanHostBatch:
+        """The same global batch as :meth:`next`, whole, on every rank: all documents in order with all their
+        tokens (layouts that cut every document over the ranks, e.g. the per-document CP baseline)."""
+        packs = self.stream.next_doc_lens()
+        ids, _labels, _pos = self.stream.next_tokens(packs)
+        return SpanHostBatch([L for p in packs for L in p], ids.reshape(-1).clone())
 
     def next(self, dp_rank: int) -> HostBatch:
         packs = self.stream.next_doc_lens()

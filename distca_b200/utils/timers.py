@@ -13,22 +13,34 @@ import torch
 
 
 class PhaseTimers:
-    def __init__(self, enabled: bool = False):
+    """``phase(name)`` brackets a piece of a step. With ``enabled`` it records a CUDA-event pair (device time,
+    read back in :meth:`summary`); with ``nvtx`` it also opens an NVTX range of that name, so a timeline shows
+    every phase of every layer and tick (the reference's per-tick / per-phase ranges,
+    distca/runtime/megatron/ping_pong/transformer_block.py:242-341)."""
+
+    def __init__(self, enabled: bool = False, nvtx: bool = False):
         self.enabled = enabled and torch.cuda.is_available()
+        self.nvtx = nvtx and torch.cuda.is_available()
         self._pairs: dict[str, list] = defaultdict(list)
 
     @contextmanager
     def phase(self, name: str):
-        if not self.enabled:
+        if not self.enabled and not self.nvtx:
             yield
             return
-        a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-        a.record()
+        if self.nvtx:
+            torch.cuda.nvtx.range_push(name)
+        if self.enabled:
+            a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            a.record()
         try:
             yield
         finally:
-            b.record()
-            self._pairs[name].append((a, b))
+            if self.enabled:
+                b.record()
+                self._pairs[name].append((a, b))
+            if self.nvtx:
+                torch.cuda.nvtx.range_pop()
 
     def summary(self, reset: bool = True) -> dict[str, float]:
         """Total milliseconds per phase since the last reset (synchronises the device)."""
@@ -46,6 +58,24 @@ GLOBAL = PhaseTimers(False)
 
 def enable(flag: bool = True) -> None:
     GLOBAL.enabled = flag and torch.cuda.is_available()
+
+
+def enable_nvtx(flag: bool = True) -> None:
+    """NVTX ranges for every phase (and, through :func:`layer`, every layer pass)."""
+    GLOBAL.nvtx = flag and torch.cuda.is_available()
+
+
+@contextmanager
+def layer(kind: str, index: int):
+    """NVTX range around one layer's forward / recompute / backward (no timing)."""
+    if not GLOBAL.nvtx:
+        yield
+        return
+    torch.cuda.nvtx.range_push(f"{kind}.layer{index}")
+    try:
+        yield
+    finally:
+        torch.cuda.nvtx.range_pop()
 
 
 def phase(name: str):

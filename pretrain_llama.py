@@ -84,7 +84,14 @@ def parse_args(argv=None):
     ap.add_argument("--comm-buffer-gb", type=float, default=float(os.environ.get("EXPERIMENT_NVSHMEM_BUFFER_SIZE_GB", 2.0)))
     ap.add_argument("--recompute", default=None, choices=["none", "selective", "full", "keep_attn"],
                     help="keep_attn (default without pipeline stages; with them: full): recompute every layer in backward except core attention, whose output is kept in HBM or pinned host memory; full: recompute whole layers; none: keep all activations")
-    ap.add_argument("--baseline-mode", default="none", choices=["none", "percp", "nccl"])
+    ap.add_argument("--baseline-mode", default="none", choices=["none", "percp"],
+                    help="percp: no core-attention disaggregation; the data-parallel ranks form a per-document "
+                         "context-parallel group instead (every document cut over all of them, K/V all-gathered, "
+                         "dK/dV reduce-scattered with NCCL): the comparison point of the reference's --mode wlbllm")
+    ap.add_argument("--tp-transport", default="p2p", choices=["p2p", "nccl"],
+                    help="tensor-parallel all-gather / reduce-scatter: fused into the GEMMs over peer memory, or NCCL")
+    ap.add_argument("--dp-transport", default="p2p", choices=["p2p", "nccl"],
+                    help="gradient reduce-scatter / parameter all-gather: fused kernels over peer memory, or NCCL")
     ap.add_argument("--attention-policy", default="cad", choices=["cad", "cp", "water_fill"],
                     help="cad: balanced core-attention disaggregation; cp: per-document context-parallel baseline")
     ap.add_argument("--tolerance", type=float, default=float(os.environ.get("MIN_TOLERANCE_FACTOR", 0.1)))
@@ -99,6 +106,7 @@ def parse_args(argv=None):
     ap.add_argument("--grad-dtype", default="bf16", choices=["bf16", "fp32"])
     ap.add_argument("--log-memory", action="store_true", default=os.environ.get("EXPERIMENT_LOG_MEMORY_USAGE", "0") == "1")
     ap.add_argument("--phase-timers", action="store_true")
+    ap.add_argument("--nvtx", action="store_true", help="NVTX ranges per step, tick, layer pass and phase")
     return ap.parse_args(argv)
 
 
@@ -130,6 +138,10 @@ def main(argv=None) -> int:
     tc.extra["tolerance"] = a.tolerance
     tc.extra["attention_policy"] = a.attention_policy
     tc.extra["baseline_mode"] = a.baseline_mode
+    tc.extra["tp_transport"] = a.tp_transport
+    tc.extra["dp_transport"] = a.dp_transport
+    if a.baseline_mode == "percp" and a.pp_size > 1:
+        raise SystemExit("--baseline-mode percp has no pipeline stages: use --pp-size 1")
     tc.extra["nano_batches"] = 2 if (a.pingpong and cad and a.pp_size == 1 and world > 1 and not a.span_documents) else 1   # ping-pong nano-batches (non-pipelined trainer)
     if a.quit_if_maybe_oom:
         import torch as _t
@@ -145,7 +157,10 @@ def main(argv=None) -> int:
     mem = MemoryLog(a.output_dir, rank, enabled=a.log_memory)
     from distca_b200.utils.observability import MetricsSink
     sink = MetricsSink(a.enable_wandb, rank, a.wandb_project, a.wandb_run_name, vars(a), a.output_dir)
-    timers.enable(a.phase_timers)
+    # with CAD the phase timers are always on: they give the exposed dispatch time and the attention time per
+    # server of every step (CUDA events only: no host synchronisation inside the step)
+    timers.enable(a.phase_timers or (cad and world > 1 and torch.cuda.is_available()))
+    timers.enable_nvtx(a.nvtx)
 
     if par.pp > 1:
         from distca_b200.parallel.pipeline import PipelineTrainer
@@ -178,14 +193,18 @@ def main(argv=None) -> int:
     from distca_b200.utils.guards import TrainingGuards
     from distca_b200.utils.profiler import ProfilerCtx
     guards = TrainingGuards(a.check_nan, a.check_for_spiky_loss, a.check_for_large_grads)
-    hb_next = src.next(trainer.dp_rank)
+    percp = a.baseline_mode == "percp" and par.dp > 1
+    draw = (lambda: src.next_global()) if percp else (lambda: src.next(trainer.dp_rank))
+    for _ in range(start_it):
+        draw()                        # resume: the data stream continues where the saved run stopped
+    hb_next = draw()
     for it in range(start_it, start_it + a.max_sample_id):
-        hb, hb_next = hb_next, src.next(trainer.dp_rank)
+        hb, hb_next = hb_next, draw()
         if a.span_documents:
             from distca_b200.runtime.trainer import make_span_batch
             hb = make_span_batch(np.random.default_rng(a.seed * 100003 + it), par.dp, a.num_tokens * a.num_batches,
                                  cfg.vocab, max_doc_len=max_len)
-        elif hasattr(trainer, "prefetch_plan"):
+        elif hasattr(trainer, "prefetch_plan") and not percp:
             trainer.prefetch_plan(hb_next)   # core attention of step it+1 is planned while step it runs
         if torch.cuda.is_available():
             torch.cuda.synchronize()
@@ -203,7 +222,10 @@ def main(argv=None) -> int:
         cad_rt = getattr(trainer, "cad", None)
         if cad_rt is not None:
             rec["attn_imbalance"] = cad_rt.plan_stats.get("imbalance_after")
-            rec["exposed_dispatch_ms"] = cad_rt.plan_stats.get("exposed_dispatch_ms")
+            rec["attn_time_imbalance_measured"] = cad_rt.plan_stats.get("attention_time_imbalance")
+            ph = timers.GLOBAL.summary(reset=not a.phase_timers) if timers.GLOBAL.enabled else {}
+            rec["exposed_dispatch_ms"] = (sum(v for k, v in ph.items() if k.startswith("cad_wait") or
+                                              k in ("cad_dispatch", "cad_return")) if ph else None)
             if cad_rt.last_plan is not None:
                 art.plan({"step": it, **inspect_plan(cad_rt.last_plan, cad_rt.W)})
         if a.phase_timers:
@@ -213,7 +235,7 @@ def main(argv=None) -> int:
         mem.log(f"step_{it}")
         log.info("step %d loss %.4f %.1f ms %.0f tok/s%s", it, loss, ms, rec["tokens_per_s"],
                  f" imbalance {rec['attn_imbalance']:.3f}" if rec.get("attn_imbalance") else "")
-        if a.val_every_n_steps and (it + 1) % a.val_every_n_steps == 0:
+        if a.val_every_n_steps and (it + 1) % a.val_every_n_steps == 0 and not percp:
             log.info("step %d validation loss %.4f", it, trainer.eval_step(hb_next))
         if save_dir and save_every and (it + 1) % save_every == 0:
             d = save_checkpoint(save_dir, it + 1, trainer.model, trainer.opt, cfg, tp_rank=trainer.tp_rank,

@@ -69,3 +69,17 @@ def test_cad_pp2_keep_attn():
     """Forward and backward of a micro-batch run under different plans; the servers keep nothing in between."""
     res = _run(2, 29547, ["--tokens", "4096", "--pp", "2", "--microbatches", "3", "--recompute", "keep_attn"])
     assert res["ok"], res
+
+
+@pytest.mark.skipif(_ngpu() < 2, reason="needs 2 GPUs")
+def test_per_document_cp_baseline_trains_like_cad():
+    """--baseline-mode percp (all-gather K/V over NCCL, no disaggregation) against CAD on the same batches."""
+    res = _run(2, 29548, ["--tokens", "8192", "--steps", "3"], check="percp")
+    assert res["ok"], res
+
+
+@pytest.mark.skipif(_ngpu() < 4, reason="needs 4 GPUs")
+def test_cad_tp2_dp2_fused_transports():
+    """Tensor parallel (GEMM-fused all-gather / reduce-scatter) x data parallel (peer reduce-scatter + Adam)."""
+    res = _run(4, 29549, ["--tokens", "8192", "--tp", "2"])
+    assert res["ok"], res
