@@ -161,10 +161,3 @@ extern "C" int dca_attn_delta_rows(const void* o, const void* dout, float* delta
   DCA_CUDA_TRY(cudaGetLastError());
   return 0;
 }
-
-#ifdef DCA_TRACE
-// Diagnostic build only: copy the dQ kernel's clock stamps to the host ([2][64][8] int64).
-extern "C" int dca_dq_trace_read(long long* dst) {
-  return (int)cudaMemcpyFromSymbol(dst, dca::attn::g_dq_trace, sizeof(long long) * 2 * 64 * 8);
-}
-#endif

@@ -46,20 +46,6 @@ constexpr int kDqBars = 1 + 2 * kDqKStages + 2 * kDqVStages + 4 * 2 + 1;
 constexpr int kDqSmemUsed = (2 + kDqKStages + kDqVStages) * 32768 + kDqBars * 8 + 16;
 constexpr int kDqSmem = kDqSmemUsed + 1024;
 
-#ifdef DCA_TRACE
-// Diagnostic build only: per-phase SM clock stamps of one CTA (compute warp 0 and the MMA warp).
-__device__ long long g_dq_trace[2][64][8];
-#define DQ_STAMP(role, j, k)                                                                 \
-  do {                                                                                       \
-    if (traced && (j) < 64) {                                                                \
-      long long t_;                                                                          \
-      asm volatile("mov.u64 %0, %%clock64;" : "=l"(t_)::"memory");                         \
-      g_dq_trace[role][j][k] = t_;                                                           \
-    }                                                                                        \
-  } while (0)
-#else
-#define DQ_STAMP(role, j, k)
-#endif
 
 struct DqParams {
   const AttnWork* work;
@@ -138,9 +124,6 @@ flash_bwd_dq_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_consta
   tc_fence_after();
   const uint32_t tmem_base = *reinterpret_cast<volatile uint32_t*>(tmem_slot);
   bool aborted = false;
-#ifdef DCA_TRACE
-  const bool traced = blockIdx.x == 0 && blockIdx.y == 0 && lane == 0 && (warp == 0 || warp == kDqCW + 1);
-#endif
 
   if (warp == kDqCW) {
     // ------------------------------ TMA producer ------------------------------
@@ -216,10 +199,8 @@ flash_bwd_dq_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_consta
             if (!mbar_wait(bar_ldp + g * 8, par, p.status)) { aborted = true; break; }
             if (!issue_dp(j + 1)) { aborted = true; break; }
           }
-          DQ_STAMP(1, j, 0);
           // dQ += dS(j) K(j); dS of keys 16kk.. sits where their scores sat: column 64 (kk/4) + 8 (kk%4)
           if (!mbar_wait(bar_dsready + g * 8, par, p.status)) { aborted = true; break; }
-          DQ_STAMP(1, j, 1);
           tc_fence_after();
           const uint64_t kb = dsc_k0t + (uint64_t)(((j % kDqKStages) * TILE) >> 4);
           const uint32_t tdS = tmem_base + g * T;
@@ -228,9 +209,7 @@ flash_bwd_dq_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_consta
             umma_ts_p(tdQ, tdS + (kk / 4) * 64 + (kk % 4) * 8, kb + (uint64_t)((kk * 2048) >> 4), idesc_dq,
                       (j > 0 || kk > 0) ? 1u : 0u, leader);
           umma_commit_p(bar_kempty + (j % kDqKStages) * 8, leader);
-          DQ_STAMP(1, j, 2);
           if (j + 2 < n_kv && !issue_s(j + 2)) { aborted = true; break; }
-          DQ_STAMP(1, j, 3);
         }
         if (!aborted) umma_commit_p(bar_dqfull, leader);
       } while (false);
@@ -255,9 +234,7 @@ flash_bwd_dq_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_consta
       const uint32_t par = (uint32_t)(j >> 1) & 1u;
       float pf[kDqCols];
       // ---- P = exp2(S * c - lse2), masked ----
-      DQ_STAMP(0, j, 0);
       if (!mbar_wait_warp(bar_sfull + g * 8, par, p.status)) { aborted = true; break; }
-      DQ_STAMP(0, j, 1);
       tc_fence_after();
       const bool full_tile = j * T + T - 1 <= w.kv_limit_base;   // every key visible to every row
 #pragma unroll
@@ -280,11 +257,8 @@ flash_bwd_dq_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_consta
           }
         }
       }
-      DQ_STAMP(0, j, 2);
       // ---- dS = P o (dP - delta) * scale as bf16, into the columns this thread read S from ----
-      DQ_STAMP(0, j, 3);
       if (!mbar_wait_warp(bar_dpfull + g * 8, par, p.status)) { aborted = true; break; }
-      DQ_STAMP(0, j, 4);
       tc_fence_after();
       // eight-column steps keep the live registers under the 96 a 576-thread CTA may use
 #pragma unroll
@@ -297,7 +271,6 @@ flash_bwd_dq_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_consta
           tc_fence_before();
           __syncwarp();
           if (lane == 0) mbar_arrive(bar_ldp + g * 8);
-          DQ_STAMP(0, j, 5);
         }
         uint32_t pk[4];
 #pragma unroll
@@ -308,12 +281,10 @@ flash_bwd_dq_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_consta
         }
         tmem_st4(tS + c0 + q8 * 4, pk);
       }
-      DQ_STAMP(0, j, 6);
       tmem_st_wait();
       tc_fence_before();
       __syncwarp();
       if (lane == 0) mbar_arrive(bar_dsready + g * 8);
-      DQ_STAMP(0, j, 7);
     }
     const int cw = warp >> 2;
     const int e0 = cw * 32;                      // epilogue: head-dim columns of this warp

@@ -6,6 +6,8 @@
 // Counterparts in the reference: TE RMSNorm fused into TELayerNormColumnParallelLinear and the TE
 // SwiGLU activation (distca/runtime/megatron/model_patch.py:77-98), Megatron bias-dropout-add
 // (distca/runtime/megatron/base_transformer_layer.py:605-608).
+#include <mutex>
+
 #include "../common/host_utils.h"
 #include "../common/ptx.cuh"
 
@@ -296,6 +298,8 @@ namespace {
 constexpr int kNoAllocMaxDevices = 64;
 float* g_noalloc_ptr[kNoAllocMaxDevices] = {nullptr};
 int g_noalloc_partials_cap[kNoAllocMaxDevices] = {0};
+int g_noalloc_setup_rc[kNoAllocMaxDevices] = {0};
+std::once_flag g_noalloc_once[kNoAllocMaxDevices];   // first calls on one device may come from several host threads
 }  // namespace
 
 extern "C" int dca_rmsnorm_bwd_noalloc(const void* x, const void* g, const float* rstd, const void* dy,
@@ -311,17 +315,24 @@ extern "C" int dca_rmsnorm_bwd_noalloc(const void* x, const void* g, const float
   int dev = -1;
   DCA_CUDA_TRY(cudaGetDevice(&dev));
   if (dev < 0 || dev >= kNoAllocMaxDevices) return kErrBadArg;
-  if (g_noalloc_ptr[dev] == nullptr) {
-    // set-up, once per device, with that device current
+  // set-up, once per device, with that device current; concurrent first calls wait here for the one that runs it
+  std::call_once(g_noalloc_once[dev], [dev]() {
     float* p = nullptr;
-    DCA_CUDA_TRY(cudaGetSymbolAddress(reinterpret_cast<void**>(&p), g_noalloc_dg_partial));
     int sms = 0;
-    DCA_CUDA_TRY(cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev));
+    cudaError_t e = cudaGetSymbolAddress(reinterpret_cast<void**>(&p), g_noalloc_dg_partial);
+    if (e == cudaSuccess) e = cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
+    if (e != cudaSuccess) {
+      fprintf(stderr, "[distca_b200] dca_rmsnorm_bwd_noalloc set-up: %s\n", cudaGetErrorString(e));
+      g_noalloc_setup_rc[dev] = (int)e;
+      return;
+    }
     g_noalloc_partials_cap[dev] = 2 * sms;
     g_noalloc_ptr[dev] = p;
-  }
+  });
+  if (g_noalloc_setup_rc[dev] != 0 || g_noalloc_ptr[dev] == nullptr) return g_noalloc_setup_rc[dev] ? g_noalloc_setup_rc[dev] : kErrBadArg;
   const int cap = g_noalloc_partials_cap[dev];
   const int P = T < cap ? T : cap;
+  if (P <= 0) return kErrBadArg;
   if (H > kNoAllocMaxH || P > kNoAllocMaxPartials) {
     fprintf(stderr,
             "[distca_b200] dca_rmsnorm_bwd_noalloc: H=%d (max %d) / %d partial rows (max %d) exceed the built-in "

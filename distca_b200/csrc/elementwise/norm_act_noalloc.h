@@ -20,7 +20,8 @@
 // Rules of use
 //  * The first call on a device looks up the array's device address (cudaGetSymbolAddress with
 //    that device current) and reads the SM count; it launches nothing else extra. Make that first
-//    call before starting any stream capture on the device.
+//    call before starting any stream capture on the device. First calls that arrive from several host
+//    threads at once are safe: the set-up runs once per device and the other callers wait for it.
 //  * The function calls no cudaMalloc, cudaFree or allocating library routine.
 //  * All calls on one device share the one array. Nothing in it has to start at zero (every launch
 //    overwrites the rows it later reads), but two calls that overlap on the GPU (different streams,

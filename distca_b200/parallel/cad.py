@@ -84,6 +84,7 @@ class CadRuntime:
         self._pending_speed = None
         self.speed = None                   # relative speed per server after the last feedback
         self._attn_events: list = []        # (start, end) CUDA events of this step's attention calls
+        self._wait_events: list = []        # ... and of its signal waits (time this rank stood idle)
         self._predicted_ms = 0.0            # what the cost model predicted for them
         self.predicted_ms = 0.0             # cost-model milliseconds (forward + backward) of the current plan on this server
 
@@ -262,40 +263,75 @@ class CadRuntime:
                 return False
         return _T()
 
-    def end_of_step_feedback(self, smoothing: float = 0.5) -> None:
-        """Collective over the attention group, called once per step after the device was synchronised:
-        every server reports measured / predicted attention time of the step; the planner's next plans give
-        server ``r`` work in proportion to its speed (GPUs under a power cap do not run at one clock, and the
-        cost model is not exact). The reference balances with fixed costs only."""
+    def _timed_wait(self):
+        """Context manager: CUDA events around one signal wait (how long this rank stood idle)."""
+        rt = self
+
+        class _T:
+            def __enter__(self_inner):
+                if rt.speed_feedback and rt.use_cost_model:
+                    self_inner.a = torch.cuda.Event(enable_timing=True)
+                    self_inner.a.record()
+                return self_inner
+
+            def __exit__(self_inner, *exc):
+                if rt.speed_feedback and rt.use_cost_model:
+                    b = torch.cuda.Event(enable_timing=True)
+                    b.record()
+                    rt._wait_events.append((self_inner.a, b))
+                return False
+        return _T()
+
+    def end_of_step_feedback(self, smoothing: float = 0.5, wait_gain: float = 0.5) -> None:
+        """Collective over the attention group, called once per step after the device was synchronised.
+        Every server reports (attention time measured, attention time predicted, time spent idle in signal
+        waits); the planner's next plans give server ``r`` the share of the attention work that would have
+        made all servers equally busy: its measured rate (predicted work per millisecond of attention: GPUs
+        under a power cap do not run at one clock, and the cost model is not exact) times the attention time
+        it can afford, i.e. what it had plus ``wait_gain`` of its idle time above the group's mean (a rank
+        whose GEMMs run slower idles less and gets less attention work). The reference balances predicted
+        FLOPs only."""
         if not (self.speed_feedback and self.use_cost_model) or self.arena is None:
             return
         measured = sum(a.elapsed_time(b) for a, b in self._attn_events)
-        predicted, self._attn_events, self._predicted_ms = self._predicted_ms, [], 0.0
+        waited = sum(a.elapsed_time(b) for a, b in self._wait_events)
+        predicted, self._attn_events, self._wait_events, self._predicted_ms = self._predicted_ms, [], [], 0.0
         import torch.distributed as dist
-        mine = torch.tensor([measured, predicted], dtype=torch.float32, device=self.device)
-        allv = torch.empty(self.W, 2, dtype=torch.float32, device=self.device)
+        mine = torch.tensor([measured, predicted, waited], dtype=torch.float32, device=self.device)
+        allv = torch.empty(self.W, 3, dtype=torch.float32, device=self.device)
         dist.all_gather_into_tensor(allv, mine, group=self.group)
         allv = allv.cpu().numpy().astype(np.float64)
-        if (allv <= 0).any():
-            return                       # a server without work this step: keep the current speeds
+        if (allv[:, :2] <= 0).any():
+            return                       # a server without work this step: keep the current shares
         self.last_measured = allv
-        speed = allv[:, 1] / allv[:, 0]          # predicted work per measured millisecond
-        speed = np.clip(speed / speed.mean(), 0.8, 1.25)
+        share = self.feedback_shares(allv[:, 0], allv[:, 1], allv[:, 2], wait_gain)
+        speed = share
         if self.speed is not None:
             speed = smoothing * speed + (1.0 - smoothing) * self.speed
         self.speed = speed / speed.mean()
+        self.plan_stats["idle_ms_per_server"] = [round(float(v), 2) for v in allv[:, 2]]
         self._pending_speed = self.speed.tolist()
         self.plan_stats["speed"] = [round(float(v), 4) for v in self.speed]
         self.plan_stats["attention_ms_per_server"] = [round(float(v), 2) for v in allv[:, 0]]
         self.plan_stats["attention_time_imbalance"] = float(allv[:, 0].max() / allv[:, 0].mean())
     # ------------------------------------------------------------------------------------------
     # server halves (every rank of the group runs them once per layer and direction)
+    @staticmethod
+    def feedback_shares(attn_ms, predicted, idle_ms, wait_gain: float = 0.5):
+        """Relative share of the attention work per server (mean 1) from one step's measurements."""
+        attn_ms, predicted, idle_ms = (np.asarray(x, dtype=np.float64) for x in (attn_ms, predicted, idle_ms))
+        rate = predicted / attn_ms                                   # work per millisecond of attention
+        afford = attn_ms + wait_gain * (idle_ms - idle_ms.mean())    # attention time that evens out the idle time
+        afford = np.maximum(afford, 0.5 * attn_ms)
+        want = rate * afford
+        return np.clip(want / want.mean(), 0.75, 1.3)
+
     def _serve_forward(self) -> None:
         self._serve_forward_begin()
         self._serve_forward_end()
 
     def _serve_forward_begin(self) -> None:
-        with timers.phase("cad_wait_qkv"):
+        with timers.phase("cad_wait_qkv"), self._timed_wait():
             self.sig.wait(SIG_QKV)
         with timers.phase("cad_attn_fwd"), self._timed_attention(self._FWD_SHARE):
             attn_ops.flash_fwd(self.Qr, self.Kr, self.Vr, self.attn_plan, out=self.AO.unflatten(1, (self.hq, self.D)),
@@ -303,7 +339,7 @@ class CadRuntime:
         self.sig.signal(SIG_OUT)
 
     def _serve_forward_end(self) -> None:
-        with timers.phase("cad_wait_out"):
+        with timers.phase("cad_wait_out"), self._timed_wait():
             self.sig.wait(SIG_OUT)
 
     def _serve_backward(self, layer: int | None = None) -> None:
@@ -311,7 +347,7 @@ class CadRuntime:
         self._serve_backward_end()
 
     def _serve_backward_begin(self, layer: int | None = None) -> None:
-        with timers.phase("cad_wait_dout"):
+        with timers.phase("cad_wait_dout"), self._timed_wait():
             self.sig.wait(SIG_DOUT)   # also covers this layer's Q/K/V rows: every owner sends them first
         nq, nk = max(self.q_rows, 1), max(self.kv_rows, 1)
         lse = self.LSE[:nq]    # sent by the owners together with dO and delta
@@ -332,7 +368,7 @@ class CadRuntime:
             self.sig.signal(SIG_DQKV)
 
     def _serve_backward_end(self) -> None:
-        with timers.phase("cad_wait_dqkv"):
+        with timers.phase("cad_wait_dqkv"), self._timed_wait():
             self.sig.wait(SIG_DQKV)
 
     # ------------------------------------------------------------------------------------------

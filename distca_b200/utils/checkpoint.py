@@ -8,7 +8,11 @@
 ``model_optim_rng.pt`` holds ``args, checkpoint_version, iteration, model, optimizer,
 opt_param_scheduler, rng_state`` with Megatron ``GPTModel`` parameter names. The fused QKV weight is
 stored the Megatron way (per KV group: its query heads, then its key head, then its value head);
-in memory this repository keeps [all Q | all K | all V] so that Q, K and V are column slices.
+in memory this repository keeps [all Q | all K | all V] so that Q, K and V are column slices; the QKV bias
+of Qwen2-style models is permuted the same way. Pipeline stages number their layers from 0 in the file
+(``decoder.layers.0`` of ``mp_rank_00_001`` is the stage's first layer), as Megatron does, while the model
+objects use global layer numbers. The random-number state saved with the model is restored on load, and the
+entry point fast-forwards its data stream by the saved iteration count.
 
 The reference's root script only saves per-rank ``torch.save`` files and has no load path
 (pretrain_llama.py:677-706, 862-863); its playground forwards Megatron's ``--save/--load``
@@ -51,23 +55,42 @@ def rank_dir(root: str, iteration: int, tp_rank: int, pp_rank: int, pp_size: int
     return os.path.join(root, f"iter_{iteration:07d}", name)
 
 
+def file_key(name: str, first_layer: int) -> str:
+    """Key of a parameter in the checkpoint file: layer numbers are local to the pipeline stage."""
+    prefix = "decoder.layers."
+    if not name.startswith(prefix):
+        return name
+    num, rest = name[len(prefix):].split(".", 1)
+    return f"{prefix}{int(num) - first_layer}.{rest}"
+
+
+def _first_layer(model) -> int:
+    return int(getattr(model, "layer_range", (0, 0))[0])
+
+
 def model_state_dict(model, cfg: ModelConfig, tp: int) -> dict:
     hq, hkv, D = cfg.heads_q // tp, cfg.heads_kv // tp, cfg.head_dim
+    first = _first_layer(model)
     sd = {}
     for name, _ in model.store.shapes:
         t = model.store.p[name].detach()
         if name.endswith("linear_qkv.weight"):
             t = qkv_to_megatron(t, hq, hkv, D)
-        sd[name] = t.cpu().clone()
+        elif name.endswith("linear_qkv.bias"):
+            t = qkv_to_megatron(t[:, None], hq, hkv, D)[:, 0]
+        sd[file_key(name, first)] = t.cpu().clone()
     return sd
 
 
 def load_model_state_dict(model, sd: dict, cfg: ModelConfig, tp: int) -> None:
     hq, hkv, D = cfg.heads_q // tp, cfg.heads_kv // tp, cfg.head_dim
+    first = _first_layer(model)
     for name, _ in model.store.shapes:
-        t = sd[name]
+        t = sd[file_key(name, first)]
         if name.endswith("linear_qkv.weight"):
             t = qkv_from_megatron(t, hq, hkv, D)
+        elif name.endswith("linear_qkv.bias"):
+            t = qkv_from_megatron(t[:, None], hq, hkv, D)[:, 0]
         model.store.p[name].copy_(t.to(model.store.p[name].dtype))
 
 
@@ -82,7 +105,7 @@ def save_checkpoint(root: str, iteration: int, model, optimizer, cfg: ModelConfi
             "iteration": iteration,
             "model": model_state_dict(model, cfg, tp_size),
             "optimizer": {"step": optimizer.step_count, "distributed": True,
-                          "param_layout": [(n, list(s)) for n, s in model.store.shapes]},
+                          "param_layout": [(file_key(n, _first_layer(model)), list(s)) for n, s in model.store.shapes]},
             "opt_param_scheduler": {"lr": optimizer.cfg.lr, "num_steps": optimizer.step_count},
             "rng_state": [{"random_rng_state": None, "torch_rng_state": torch.get_rng_state(),
                            "cuda_rng_state": torch.cuda.get_rng_state() if torch.cuda.is_available() else None}],
@@ -119,4 +142,10 @@ def load_checkpoint(root: str, model, optimizer, cfg: ModelConfig, *, tp_rank: i
         optimizer.load_state_dict(torch.load(opt_path, map_location="cpu", weights_only=False))
     elif optimizer is not None and hasattr(optimizer, "resync_master"):
         optimizer.resync_master()     # weights only: rebuild the fp32 master copy from them
+    rng = (payload.get("rng_state") or [None])[0]
+    if rng:
+        if rng.get("torch_rng_state") is not None:
+            torch.set_rng_state(rng["torch_rng_state"])
+        if rng.get("cuda_rng_state") is not None and torch.cuda.is_available():
+            torch.cuda.set_rng_state(rng["cuda_rng_state"])
     return int(payload["iteration"])

@@ -136,3 +136,16 @@ def test_tables_built_on_a_worker_thread_equal_the_direct_ones():
         assert torch.equal(getattr(direct, name), getattr(ahead, name)), name
     assert direct.plan_stats == ahead.plan_stats and direct.Tcur == ahead.Tcur == T
     assert np.array_equal(direct.attn_plan.bwd_qt_host, ahead.attn_plan.bwd_qt_host)
+
+
+def test_feedback_shares_move_work_towards_idle_servers():
+    """One step's measurements -> next step's shares of the attention work: a server that idled less than the
+    others (its other kernels ran slower) or that needed longer for the same predicted work gets a smaller share."""
+    import numpy as np
+    even = CadRuntime.feedback_shares([100] * 4, [100] * 4, [10] * 4)
+    assert np.allclose(even, 1.0)
+    slow_gemms = CadRuntime.feedback_shares([100] * 4, [100] * 4, [10, 10, 10, 0])
+    assert slow_gemms[3] < 0.98 and np.all(slow_gemms[:3] > 1.0) and abs(slow_gemms.mean() - 1.0) < 1e-9
+    slow_attention = CadRuntime.feedback_shares([100, 100, 100, 125], [100] * 4, [20, 20, 20, 0])
+    assert slow_attention[3] < slow_gemms[3]
+    assert np.all(CadRuntime.feedback_shares([1, 1, 1, 100], [1] * 4, [0] * 4) >= 0.75)      # bounded

@@ -48,3 +48,55 @@ def test_qkv_layout_roundtrip():
     assert torch.equal(m[:g * D], w[:g * D])
     assert torch.equal(m[g * D:(g + 1) * D], w[hq * D:hq * D + D])
     assert torch.equal(m[(g + 1) * D:(g + 2) * D], w[(hq + hkv) * D:(hq + hkv) * D + D])
+
+
+def test_pipeline_stage_and_qkv_bias_checkpoints_use_megatron_keys():
+    """Round trip against a hand-built state dict with Megatron keys: a pipeline stage's file numbers its
+    layers from 0, and the QKV bias of a Qwen2-style model is stored per KV group like the weight."""
+    from distca_b200.models.config import ModelConfig
+    from distca_b200.models.llama import LlamaModel
+    from distca_b200.utils.checkpoint import (file_key, load_model_state_dict, model_state_dict, qkv_from_megatron,
+                                              qkv_to_megatron)
+    cfg = ModelConfig(name="q", num_layers=4, hidden=32, heads_q=4, heads_kv=2, head_dim=8, ffn=48, vocab=64,
+                      qkv_bias=True, max_position=64)
+    hq, hkv, D = cfg.heads_q, cfg.heads_kv, cfg.head_dim
+    # second stage of two: global layers 2 and 3
+    stage = LlamaModel(cfg, "cpu", layer_range=(2, 4), first_stage=False, last_stage=True, dtype=torch.float32, seed=3)
+    sd = model_state_dict(stage, cfg, tp=1)
+    assert "decoder.layers.0.self_attention.linear_qkv.weight" in sd and "decoder.layers.1.mlp.linear_fc2.weight" in sd
+    assert not any(k.startswith("decoder.layers.2.") or k.startswith("decoder.layers.3.") for k in sd)
+    assert file_key("decoder.layers.3.mlp.linear_fc1.weight", 2) == "decoder.layers.1.mlp.linear_fc1.weight"
+    assert file_key("output_layer.weight", 2) == "output_layer.weight"
+    # the bias is permuted exactly like the rows of the weight
+    b = stage.store.p["decoder.layers.2.self_attention.linear_qkv.bias"]
+    w = stage.store.p["decoder.layers.2.self_attention.linear_qkv.weight"]
+    assert torch.equal(sd["decoder.layers.0.self_attention.linear_qkv.bias"], qkv_to_megatron(b[:, None], hq, hkv, D)[:, 0])
+    g = hq // hkv
+    assert torch.equal(sd["decoder.layers.0.self_attention.linear_qkv.bias"][g * D:(g + 1) * D], b[hq * D:hq * D + D])
+    assert torch.equal(sd["decoder.layers.0.self_attention.linear_qkv.weight"], qkv_to_megatron(w, hq, hkv, D))
+    # a state dict written by hand with Megatron keys loads into the right global layers
+    hand = {k: torch.randn_like(v) for k, v in sd.items()}
+    other = LlamaModel(cfg, "cpu", layer_range=(2, 4), first_stage=False, last_stage=True, dtype=torch.float32, seed=9)
+    load_model_state_dict(other, hand, cfg, tp=1)
+    torch.testing.assert_close(other.store.p["decoder.layers.3.mlp.linear_fc2.weight"], hand["decoder.layers.1.mlp.linear_fc2.weight"])
+    torch.testing.assert_close(other.store.p["decoder.layers.2.self_attention.linear_qkv.bias"],
+                               qkv_from_megatron(hand["decoder.layers.0.self_attention.linear_qkv.bias"][:, None], hq, hkv, D)[:, 0])
+    for k, v in model_state_dict(other, cfg, tp=1).items():
+        torch.testing.assert_close(v, hand[k])
+
+
+def test_checkpoint_restores_rng_state(tmp_path):
+    from distca_b200.models.config import ModelConfig, TrainConfig
+    from distca_b200.models.llama import LlamaModel
+    from distca_b200.parallel.optimizer import ShardedAdam
+    from distca_b200.utils.checkpoint import load_checkpoint, save_checkpoint
+    cfg = ModelConfig(name="r", num_layers=1, hidden=32, heads_q=2, heads_kv=1, head_dim=16, ffn=48, vocab=64, max_position=64)
+    m = LlamaModel(cfg, "cpu", dtype=torch.float32)
+    opt = ShardedAdam(m.store, TrainConfig())
+    torch.manual_seed(1234)
+    torch.rand(3)
+    save_checkpoint(str(tmp_path), 5, m, opt, cfg)
+    want = torch.rand(4)
+    torch.manual_seed(99)
+    assert load_checkpoint(str(tmp_path), m, opt, cfg) == 5
+    assert torch.equal(torch.rand(4), want)
