@@ -56,6 +56,9 @@ struct DqParams {
   long Tq;
   __nv_bfloat16* dq;    // [Tq, ld_dq]
   long ld_dq;
+  // Optional: address of the dQ row (head 0) of every Q row, e.g. in the token owner's arena on another GPU
+  // (plain peer stores over NVLink); 0 = row not stored. Replaces dq / ld_dq when given.
+  const unsigned long long* dq_row_ptr;
   unsigned int* status;
 };
 
@@ -295,8 +298,12 @@ flash_bwd_dq_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_consta
         uint32_t a[32];
         tmem_ld32(tdQ + e0, a);
         tmem_ld_wait();
-        if (row_ok) {
-          __nv_bfloat16* dst = p.dq + ((long)w.q_row0 + r) * p.ld_dq + (long)head * D + e0;
+        unsigned long long rowp = 1ull;
+        if (row_ok && p.dq_row_ptr != nullptr) rowp = p.dq_row_ptr[(long)w.q_row0 + r];
+        if (row_ok && rowp != 0ull) {
+          __nv_bfloat16* dst = p.dq_row_ptr != nullptr
+                                   ? reinterpret_cast<__nv_bfloat16*>(rowp) + (long)head * D + e0
+                                   : p.dq + ((long)w.q_row0 + r) * p.ld_dq + (long)head * D + e0;
 #pragma unroll
           for (int v = 0; v < 4; ++v) {
             uint4 u;

@@ -553,6 +553,7 @@ class LlamaModel:
         self._store = None
         self._stores = None
         self._pinned = []
+        self.grad_ready_hook = None        # called with a layer's parameter names once its gradients are final
         self.store_sync_group = None       # gloo-capable group over which the keep_attn placement is agreed
         self.attn_store_placement = None   # "device" | "host" to override the automatic choice
 
@@ -723,6 +724,8 @@ class LlamaModel:
             with timers.layer("bwd", layer.index):
                 dx = layer.backward(ctx, dx, batch.pos, self.rope_table, core_attn)
             del ctx
+            if self.grad_ready_hook is not None:
+                self.grad_ready_hook(list(layer.names.values()))
         with timers.phase("embed_bwd"):
             self.embed_bwd(batch.ids, dx)
         return loss, None
@@ -776,6 +779,8 @@ class LlamaModel:
             with timers.layer("bwd", layer.index):
                 dxs = layer.backward_nano(cs, dxs, poss, self.rope_table, cas)
             del cs
+            if self.grad_ready_hook is not None:
+                self.grad_ready_hook(list(layer.names.values()))
         with timers.phase("embed_bwd"):
             for k in range(n):
                 if dxs[k] is not None:
@@ -816,9 +821,11 @@ class LlamaModel:
             ctxs.append(ctx)
         return x, (inputs, ctxs, x if self.last_stage else None, store)
 
-    def stage_backward(self, batch: Batch, core_attn, saved, dy: torch.Tensor | None):
+    def stage_backward(self, batch: Batch, core_attn, saved, dy: torch.Tensor | None, grads_final: bool = False):
         """Backward of this stage for one micro-batch. On the last stage ``dy`` is ignored and the
-        loss head produces the gradient. Returns ``(loss or None, dx for the previous stage or None)``."""
+        loss head produces the gradient. ``grads_final``: this is the step's last micro-batch, so a layer's
+        gradients are complete once its backward has run (the gradient-ready hook fires per layer).
+        Returns ``(loss or None, dx for the previous stage or None)``."""
         inputs, ctxs, x_out, store = saved
         loss = None
         if self.last_stage:
@@ -839,6 +846,8 @@ class LlamaModel:
             with timers.layer("bwd", layer.index):
                 dx = layer.backward(ctx, dx, batch.pos, self.rope_table, core_attn)
             del ctx
+            if grads_final and self.grad_ready_hook is not None:
+                self.grad_ready_hook(list(layer.names.values()))
         if self.first_stage:
             with timers.phase("embed_bwd"):
                 self.embed_bwd(batch.ids, dx)

@@ -277,10 +277,14 @@ _DEFAULT_SCRATCH = BwdScratch()
 
 def flash_bwd(q, k, v, o, lse, dout, plan: AttnPlan, scale: float | None = None,
               dq=None, dk=None, dv=None, scratch: BwdScratch | None = None,
-              delta_rows: torch.Tensor | None = None):
+              delta_rows: torch.Tensor | None = None, dq_row_ptr: torch.Tensor | None = None,
+              dkv_row_ptr: torch.Tensor | None = None, dv_off_bytes: int = 0):
     """Gradients of :func:`flash_fwd`. ``dk``/``dv`` rows not covered by any task are left as given
     (pass zero-filled tensors when such rows exist). With ``delta_rows`` (fp32 [Tq, Hq] =
     rowsum(dO o O), see :func:`attn_delta_rows`) ``o`` is not read and may be ``None``.
+    With ``dq_row_ptr`` [Tq] / ``dkv_row_ptr`` [Tk] (device int64 addresses, 0 = skip the row) the kernels store
+    every gradient row straight to that address (head 0 of the row; dV ``dv_off_bytes`` behind dK), e.g. into the
+    token owners' arenas on other GPUs, and ``dq`` / ``dk`` / ``dv`` are not written.
     Returns ``(dq, dk, dv)``."""
     Tq, Hq, D = q.shape
     Tk, Hkv, _ = k.shape
@@ -295,14 +299,16 @@ def flash_bwd(q, k, v, o, lse, dout, plan: AttnPlan, scale: float | None = None,
             dv.copy_(gv); gv = dv
         return gq, gk, gv
     dev = q.device
-    if dq is None:
+    if dq is None and dq_row_ptr is None:
         dq = torch.empty(Tq, Hq, D, dtype=torch.bfloat16, device=dev)
-    if dk is None:
+    if dk is None and dkv_row_ptr is None:
         dk = torch.zeros(Tk, Hkv, D, dtype=torch.bfloat16, device=dev)
-    if dv is None:
+    if dv is None and dkv_row_ptr is None:
         dv = torch.zeros(Tk, Hkv, D, dtype=torch.bfloat16, device=dev)
-    for t in (q, k, v, dout, dq, dk, dv) + (() if o is None else (o,)):
-        assert t.dtype == torch.bfloat16 and t.stride(2) == 1 and t.stride(1) == D
+    for t in (q, k, v, dout, dq, dk, dv, o):
+        assert t is None or (t.dtype == torch.bfloat16 and t.stride(2) == 1 and t.stride(1) == D)
+    assert dq_row_ptr is None or (dq_row_ptr.dtype == torch.int64 and dq_row_ptr.numel() >= Tq)
+    assert dkv_row_ptr is None or (dkv_row_ptr.dtype == torch.int64 and dkv_row_ptr.numel() >= Tk)
     delta, lse2 = (scratch or _DEFAULT_SCRATCH).get(Tq, Hq, D, dev)
     L = _lib.lib()
     rc = L.dca_flash_bwd(
@@ -313,9 +319,10 @@ def flash_bwd(q, k, v, o, lse, dout, plan: AttnPlan, scale: float | None = None,
         _lib.ptr(plan.bwd_kv_dev), _lib.c_int(plan.num_bwd), _lib.ptr(plan.bwd_qt_dev),
         _lib.ptr(plan.fwd_plain_dev), _lib.c_int(plan.num_fwd),
         _lib.c_float(scale), _lib.ptr(delta), _lib.ptr(lse2),
-        _lib.ptr(dq), _lib.c_long(dq.stride(0)), _lib.ptr(dk), _lib.c_long(dk.stride(0)),
-        _lib.ptr(dv), _lib.c_long(dv.stride(0)), _lib.ptr(delta_rows),
-        _lib.c_long(0 if delta_rows is None else delta_rows.stride(0)),
+        _lib.ptr(dq), _lib.c_long(0 if dq is None else dq.stride(0)), _lib.ptr(dk),
+        _lib.c_long(0 if dk is None else dk.stride(0)), _lib.ptr(dv), _lib.c_long(0 if dv is None else dv.stride(0)),
+        _lib.ptr(delta_rows), _lib.c_long(0 if delta_rows is None else delta_rows.stride(0)),
+        _lib.ptr(dq_row_ptr), _lib.ptr(dkv_row_ptr), _lib.c_long(dv_off_bytes),
         _lib.ptr(_lib.status_word(dev)), _lib.stream_ptr())
     _lib.check_rc(rc, "flash_bwd")
     return dq, dk, dv
@@ -336,3 +343,17 @@ def attn_delta_rows(o: torch.Tensor, dout: torch.Tensor, out: torch.Tensor | Non
                                         _lib.c_long(out.stride(0)), _lib.stream_ptr())
     _lib.check_rc(rc, "attn_delta_rows")
     return out
+
+
+def dispatch_dout(o: torch.Tensor, dout: torch.Tensor, lse: torch.Tensor, do_dst: torch.Tensor, do_off_bytes: int,
+                  delta_dst: torch.Tensor, lse_dst: torch.Tensor) -> None:
+    """Owner half of the backward dispatch as one kernel: ``delta = rowsum(dO o O)`` per head, then the dO row,
+    the delta row and the log-sum-exp row of every token are stored at that token's destinations
+    (``do_dst[t] + do_off_bytes``, ``delta_dst[t]``, ``lse_dst[t]``: device int64 addresses, possibly in other
+    GPUs' arenas; 0 in ``do_dst`` skips the token). ``o`` / ``dout``: [T, Hq, 128] bf16; ``lse``: [T, Hq] fp32."""
+    T, Hq, D = dout.shape
+    rc = _lib.lib().dca_dispatch_dout(_lib.ptr(o), _lib.ptr(dout), _lib.ptr(lse), _lib.c_long(T), _lib.c_int(Hq),
+                                      _lib.c_int(D), _lib.c_long(o.stride(0)), _lib.c_long(dout.stride(0)),
+                                      _lib.c_long(lse.stride(0)), _lib.ptr(do_dst), _lib.c_long(do_off_bytes),
+                                      _lib.ptr(delta_dst), _lib.ptr(lse_dst), _lib.stream_ptr())
+    _lib.check_rc(rc, "dispatch_dout")

@@ -351,20 +351,28 @@ class CadRuntime:
             self.sig.wait(SIG_DOUT)   # also covers this layer's Q/K/V rows: every owner sends them first
         nq, nk = max(self.q_rows, 1), max(self.kv_rows, 1)
         lse = self.LSE[:nq]    # sent by the owners together with dO and delta
-        dq = torch.empty(nq, self.hq, self.D, dtype=torch.bfloat16, device=self.device)
-        dk = torch.empty(nk, self.hkv, self.D, dtype=torch.bfloat16, device=self.device)
-        dv = torch.empty(nk, self.hkv, self.D, dtype=torch.bfloat16, device=self.device)
+        fused = bool(self.tcfg.extra.get("fuse_grad_return", True))
         with timers.phase("cad_attn_bwd"), self._timed_attention(1.0 - self._FWD_SHARE):
-            if self.q_rows:
+            if self.q_rows and fused:
+                # the backward kernels store every dQ row and every dK / dV row straight into its owner's arena
+                # (DQKV rows / copy slots, peer stores over NVLink) from their epilogues: nothing is staged
+                # on the server and no scatter pass follows
+                attn_ops.flash_bwd(self.Qr[:nq], self.Kr[:nk], self.Vr[:nk], None, lse, self.dOr[:nq],
+                                   self.attn_plan, scratch=self.scratch, delta_rows=self.DELTAr[:nq],
+                                   dq_row_ptr=self.q_ret, dkv_row_ptr=self.kv_ret, dv_off_bytes=self.kv_bytes)
+            elif self.q_rows:
+                dq = torch.empty(nq, self.hq, self.D, dtype=torch.bfloat16, device=self.device)
+                dk = torch.empty(nk, self.hkv, self.D, dtype=torch.bfloat16, device=self.device)
+                dv = torch.empty(nk, self.hkv, self.D, dtype=torch.bfloat16, device=self.device)
                 attn_ops.flash_bwd(self.Qr[:nq], self.Kr[:nk], self.Vr[:nk], None, lse, self.dOr[:nq],
                                    self.attn_plan, dq=dq, dk=dk, dv=dv, scratch=self.scratch,
                                    delta_rows=self.DELTAr[:nq])
         with timers.phase("cad_return"):
-            if self.q_rows:
+            if self.q_rows and not fused:
                 scatter_rows(dq.flatten(1)[:self.q_rows], self.q_bytes, self.q_ret)
-            if self.kv_rows:
-                scatter_rows(dk.flatten(1)[:self.kv_rows], self.kv_bytes, self.kv_ret)
-                scatter_rows(dv.flatten(1)[:self.kv_rows], self.kv_bytes, self.kv_ret, self.kv_bytes)
+                if self.kv_rows:
+                    scatter_rows(dk.flatten(1)[:self.kv_rows], self.kv_bytes, self.kv_ret)
+                    scatter_rows(dv.flatten(1)[:self.kv_rows], self.kv_bytes, self.kv_ret, self.kv_bytes)
             self.sig.signal(SIG_DQKV)
 
     def _serve_backward_end(self) -> None:
@@ -433,11 +441,16 @@ class CadRuntime:
         if T:
             o, lse = ctx if ctx is not None else (self.AO[:T], self.LSEo[:T])
             with timers.phase("cad_dispatch"):
-                delta = attn_ops.attn_delta_rows(o.unflatten(1, (self.hq, self.D)),
-                                                 dattn.unflatten(1, (self.hq, self.D)))
-                scatter_rows(dattn, self.q_bytes, self.q_dst, self.off["dOr"] - self.off["Qr"])
-                scatter_rows(delta, self.hq * 4, self.delta_dst)
-                scatter_rows(lse, self.hq * 4, self.lse_dst)
+                if self.tcfg.extra.get("fuse_dout_dispatch", True) and lse.stride(1) == 1:
+                    # one kernel: delta = rowsum(dO o O), then dO / delta / LSE rows stored at the servers
+                    attn_ops.dispatch_dout(o.unflatten(1, (self.hq, self.D)), dattn.unflatten(1, (self.hq, self.D)), lse,
+                                           self.q_dst, self.off["dOr"] - self.off["Qr"], self.delta_dst, self.lse_dst)
+                else:
+                    delta = attn_ops.attn_delta_rows(o.unflatten(1, (self.hq, self.D)),
+                                                     dattn.unflatten(1, (self.hq, self.D)))
+                    scatter_rows(dattn, self.q_bytes, self.q_dst, self.off["dOr"] - self.off["Qr"])
+                    scatter_rows(delta, self.hq * 4, self.delta_dst)
+                    scatter_rows(lse, self.hq * 4, self.lse_dst)
         self.sig.signal(SIG_DOUT)
 
     def backward_serve(self, layer: int = 0) -> None:

@@ -29,7 +29,8 @@ class PeerDataParallel:
         self.grad_dtype = grad_dtype
         self.arena = PeerArena(nbytes + gbytes + (1 << 20), group, device)
         self.size, self.rank = self.arena.size, self.arena.rank
-        self.sig = SignalBoard(self.arena, 2)
+        self.sig = SignalBoard(self.arena, 3)      # 0: backward complete, 1: parameters pushed, 2: bucket complete
+        self.side = torch.cuda.Stream(self.device)  # bucket reductions run here, beside the rest of backward
         self.off_param = self.arena.alloc(nbytes, align=4096)
         self.off_grad = self.arena.alloc(gbytes, align=4096)
         self.flat = self.arena.view(self.off_param, (numel,), torch.bfloat16)
@@ -48,6 +49,31 @@ class PeerDataParallel:
         rc = fn(_lib.ptr(self.grad_tbl), _lib.c_int(self.size), _lib.c_int(self.rank),
                 _lib.c_long(lo), _lib.c_long(n), _lib.ptr(sumsq), _lib.stream_ptr())
         _lib.check_rc(rc, "reduce_scatter_sumsq")
+
+    def _reduce(self, lo: int, n: int, sumsq: torch.Tensor) -> None:
+        fn = (_lib.lib().dca_reduce_scatter_sumsq_f32 if self.grad_dtype == torch.float32
+              else _lib.lib().dca_reduce_scatter_sumsq_bf16)
+        rc = fn(_lib.ptr(self.grad_tbl), _lib.c_int(self.size), _lib.c_int(self.rank),
+                _lib.c_long(lo), _lib.c_long(n), _lib.ptr(sumsq), _lib.stream_ptr())
+        _lib.check_rc(rc, "reduce_scatter_sumsq")
+
+    def bucket_ready(self, ranges: list[tuple[int, int]], sumsq: torch.Tensor) -> None:
+        """The gradients of one bucket (a layer) are final on this rank: on the side stream, tell the peers,
+        wait until theirs are final too, and reduce the parts ``ranges`` = [(lo, n), ...] of the bucket that
+        belong to this rank's shard (possibly none), while the main stream goes on with the next layer's
+        backward. Every rank calls this for every bucket, in the same order."""
+        ev = torch.cuda.Event()
+        ev.record()
+        with torch.cuda.stream(self.side):
+            self.side.wait_event(ev)
+            self.sig.signal(2)
+            self.sig.wait(2)
+            for lo, n in ranges:
+                self._reduce(lo, n, sumsq)
+
+    def join_buckets(self) -> None:
+        """Make the current stream wait for the bucket reductions queued so far."""
+        torch.cuda.current_stream(self.device).wait_stream(self.side)
 
     def adam_push(self, pshard, lo16, gshard, m, v, lo: int, *, lr, beta1, beta2, eps, weight_decay, step, gscale) -> None:
         rc = _lib.lib().dca_adam_push(_lib.ptr(pshard), _lib.ptr(lo16), _lib.ptr(gshard),

@@ -51,6 +51,12 @@ class ShardedAdam:
                 o, k = store.offsets[n]
                 self._dup_ranges.append((o, o + k))
         self.last_grad_norm = None
+        # gradient reduce-scatter in buckets while backward still runs (peer transport only)
+        # (not with tensor parallelism: the replicated norm-weight gradients are first summed over the
+        # tensor-parallel group at the end of backward, and the data-parallel reduction has to follow that)
+        self.bucketed = (self.p2p is not None and self.dp > 1 and not replicated_names
+                         and bool(cfg.extra.get("dp_buckets", True)))
+        self._reduced: list[tuple[int, int]] = []      # [lo, hi) ranges of this step already reduced
         if self.dp > 1 and store.grad.dtype != torch.float32 and self.p2p is None:
             self._rs_out = torch.empty(self.shard, dtype=store.grad.dtype, device=dev)
         else:
@@ -89,12 +95,58 @@ class ShardedAdam:
         else:
             self.gscale.fill_(1.0)
 
+    def begin_step(self) -> None:
+        """Call once per step before any gradient is produced (next to ``zero_grad``)."""
+        if self.bucketed:
+            self.sumsq.zero_()
+            self._reduced = []
+
+    def bucket_ready(self, names) -> None:
+        """The gradients of the parameters ``names`` (one layer: a contiguous range of the flat buffer) are
+        final for this step: their part of this rank's shard is reduce-scattered now, on a side stream, while
+        the backward pass goes on (the reference leaves this to Megatron's DistributedOptimizer with
+        ``overlap_grad_reduce`` off, distca/utils/megatron_test_utils.py:235-258). Every rank calls it for the
+        same buckets in the same order."""
+        if not self.bucketed:
+            return
+        lo = min(self.store.offsets[n][0] for n in names)
+        hi = max(self.store.offsets[n][0] + self.store.offsets[n][1] for n in names)
+        hi = (hi + ParamStore.ALIGN - 1) // ParamStore.ALIGN * ParamStore.ALIGN
+        a, b = max(lo, self.lo), min(hi, self.hi)
+        ranges = []
+        if b > a:
+            ranges.append((a, b - a))
+            self._reduced.append((a, b))
+        self.p2p.bucket_ready(ranges, self.sumsq)
+
+    def _remaining(self) -> list[tuple[int, int]]:
+        """Parts of this rank's shard that no bucket has reduced yet, as (lo, n)."""
+        out, cur = [], self.lo
+        for a, b in sorted(self._reduced):
+            if a > cur:
+                out.append((cur, a - cur))
+            cur = max(cur, b)
+        if cur < self.hi:
+            out.append((cur, self.hi - cur))
+        return out
+
     def _step_peer(self) -> None:
         """Steps 1-4 on peer memory: reduce-scatter fused with the norm partial, Adam fused with the
         parameter all-gather (see :mod:`distca_b200.parallel.dp_p2p`)."""
         c = self.cfg
-        self.sumsq.zero_()
-        self.p2p.reduce_scatter_sumsq(self.lo, self.shard, self.sumsq)
+        if self.bucketed:
+            # the layers were reduced as backward produced them; what is left (embedding, final norm, LM head)
+            # follows here, after every rank's backward has ended
+            self.p2p.join_buckets()
+            rest = self._remaining()
+            self._reduced = []
+            self.p2p.sig.signal(0)
+            self.p2p.sig.wait(0)
+            for lo, n in rest:
+                self.p2p._reduce(lo, n, self.sumsq)
+        else:
+            self.sumsq.zero_()
+            self.p2p.reduce_scatter_sumsq(self.lo, self.shard, self.sumsq)
         gshard = self.store.grad[self.lo:self.hi]
         for a, b in self._dup_ranges:
             a2, b2 = max(a, self.lo) - self.lo, min(b, self.hi) - self.lo

@@ -106,6 +106,8 @@ class PipelineTrainer:
         self.opt = ShardedAdam(self.model.store, train_cfg, dp_group=self.groups.dp_group if par.dp > 1 else None,
                                norm_group=self.groups.world_group, replicated_names=repl if par.tp > 1 else (),
                                tp_rank=self.tp_rank, p2p=self.p2p)
+        if self.opt.bucketed:
+            self.model.grad_ready_hook = self.opt.bucket_ready
         self.prev = par.rank_of(self.tp_rank, self.dp_rank, self.pp_rank - 1) if not self.first else None
         self.next = par.rank_of(self.tp_rank, self.dp_rank, self.pp_rank + 1) if not self.last else None
         self.act_dtype = self.model.dtype
@@ -203,6 +205,7 @@ class PipelineTrainer:
         from ..utils.observability import nvtx_range
         M, pp, p = self.M, self.par.pp, self.pp_rank
         self.model.store.zero_grad()
+        self.opt.begin_step()
         T, all_mb_docs, batches = self._split_microbatches(hb)
         if self.par.tp > 1:
             self.model.tp.ensure_fused(T // self.par.tp)
@@ -255,7 +258,8 @@ class PipelineTrainer:
                     dx = None
                     if 0 <= b_mb < M:
                         real += 1
-                        loss, dx = self.model.stage_backward(batches[b_mb], ca, saved.pop(b_mb), dy_in)
+                        loss, dx = self.model.stage_backward(batches[b_mb], ca, saved.pop(b_mb), dy_in,
+                                                             grads_final=(b_mb == M - 1))
                         if loss is not None:
                             loss_sum += loss
                     elif self.cad is not None:

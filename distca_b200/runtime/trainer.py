@@ -223,6 +223,8 @@ class Trainer:
                                dp_group=self.groups.dp_group if self.groups and par.dp > 1 else None,
                                norm_group=self.groups.world_group if self.groups else None,
                                replicated_names=repl if par.tp > 1 else (), tp_rank=self.tp_rank, p2p=self.p2p)
+        if self.opt.bucketed:
+            self.model.grad_ready_hook = self.opt.bucket_ready
         self.step_idx = 0
         self.timers: dict[str, float] = {}
         from ..utils.watchdog import StepGuard
@@ -309,6 +311,7 @@ class Trainer:
         from ..utils import timers
         with timers.phase("zero_grad"):
             self.model.store.zero_grad()
+            self.opt.begin_step()
         self.model.ensure_positions(max(hb.doc_lens, default=0))
         assert self.percp is None or isinstance(hb, SpanHostBatch), \
             "the per-document CP baseline takes the global batch (BatchSource.next_global)"
@@ -374,6 +377,7 @@ class Trainer:
         """Same step with the batch already on the device and the plan built; returns the loss as a
         device tensor (no host synchronisation). Used for device-only timing."""
         self.model.store.zero_grad()
+        self.opt.begin_step()
         self.model.ensure_positions(max(hb.doc_lens, default=0))
         if self.par.tp > 1:
             self.model.tp.ensure_fused(hb.ids.numel() // self.par.tp)

@@ -226,6 +226,27 @@ def test_flash_attention_fwd_bwd(name, tasks, Tq, Tk, Hq, Hkv):
     # arrival order, so two runs may differ in the last bit
     assert torch.equal(dk2, dk) and torch.equal(dv2, dv)
     assert (dq2.float() - dq.float())[mask].abs().max().item() <= 1e-2 * dq.float()[mask].abs().max().item()
+    # gradient rows stored through per-row destination addresses (the epilogues' store-to-owner path):
+    # rows land permuted in other buffers, dV behind dK in one [K | V] row; an address of 0 skips the row
+    qperm, kperm = torch.randperm(Tq, device="cuda"), torch.randperm(Tk, device="cuda")
+    dq_buf = torch.zeros(Tq, Hq * D, dtype=torch.bfloat16, device="cuda")
+    dkv_buf = torch.zeros(Tk, 2 * Hkv * D, dtype=torch.bfloat16, device="cuda")
+    q_ptr = dq_buf.data_ptr() + qperm * (Hq * D * 2)
+    kv_ptr = dkv_buf.data_ptr() + kperm * (2 * Hkv * D * 2)
+    kv_ptr[3] = 0
+    A.flash_bwd(q, k, v, None, lse, do, plan, delta_rows=delta, dq_row_ptr=q_ptr, dkv_row_ptr=kv_ptr,
+                dv_off_bytes=Hkv * D * 2)
+    _lib.check_status()
+    got_dq = dq_buf[qperm].unflatten(1, (Hq, D))
+    got_kv = dkv_buf[kperm]
+    got_dk, got_dv = got_kv[:, :Hkv * D].unflatten(1, (Hkv, D)), got_kv[:, Hkv * D:].unflatten(1, (Hkv, D))
+    assert (got_dq.float() - dq.float())[mask].abs().max().item() <= 1e-2 * dq.float()[mask].abs().max().item()
+    kmask = torch.zeros(Tk, dtype=torch.bool, device="cuda")
+    for ks, kl in zip(t.k_start, t.kv_len):
+        kmask[int(ks):int(ks) + int(kl)] = True
+    kmask[3] = False
+    assert torch.equal(got_dk[kmask], dk[kmask]) and torch.equal(got_dv[kmask], dv[kmask])
+    assert got_kv[3].abs().max().item() == 0
 
 
 # ---------------------------------------------------------------- peer-memory helpers on one GPU
