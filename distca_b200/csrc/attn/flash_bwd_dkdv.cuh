@@ -24,12 +24,6 @@
 // behind dV(i) and dP^T(i+1) right behind dK(i) (tcgen05.mma executes in issue order, so the
 // overwritten P^T / dS^T have been consumed).
 //
-// Every product is issued as two HALVES over the query dimension (queries 0-63 = half 0, 64-127 = half 1;
-// S^T / dP^T with N = 64, dV / dK with four of the eight 16-query K steps each), with their own barriers and
-// their own eight compute warps. S^T(i+1) of a half must wait for that half's P^T(i) -> dV(i) only, so the
-// exponentials of one half run while the tensor core works on the other half: with whole tiles the loop
-// "S^T done -> 16K exponentials -> dV -> next S^T" left the tensor pipe idle about 30 % of the time.
-//
 // TMEM columns: [0,128) S^T / P^T, [128,256) dP^T / dS^T, [256,384) dV, [384,512) dK.
 // Warps 0-15 compute (TMEM lane quarter = warp % 4; warp group warp / 4 owns query columns
 // 32 * (warp / 4) .. + 31; four warps per scheduler hide one another's TMEM-load, exponential and
@@ -48,7 +42,7 @@ constexpr int kBwdThreads = (kBwdCW + 2) * 32;
 constexpr int kBT = 128;                    // tile edge (keys, queries)
 constexpr int kBD = 128;                    // head dim
 constexpr int kTileB = kBT * kBD * 2;       // 32 KiB
-constexpr int kDkdvBars = 20;
+constexpr int kDkdvBars = 18;
 // K, V, 2 x (Q | dO), 2 x (lse, delta), barriers, tmem slot, alignment slack
 constexpr int kDkdvSmemUsed = 6 * kTileB + 2048 + kDkdvBars * 8 + 16;
 constexpr int kDkdvSmem = kDkdvSmemUsed + 1024;
@@ -92,17 +86,18 @@ flash_bwd_dkdv_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_cons
   float* s_stats = reinterpret_cast<float*>(smem + 6 * kTileB);  // [2][lse 128 | delta 128]
   uint64_t* bars = reinterpret_cast<uint64_t*>(smem + 6 * kTileB + 2048);
   const uint32_t bar_kv = smem_u32(bars);
-  const uint32_t bar_qfull = bar_kv + 8;          // [2] by stage
+  const uint32_t bar_qfull = bar_kv + 8;          // [2]
   const uint32_t bar_dofull = bar_qfull + 16;     // [2]
   const uint32_t bar_qdoempty = bar_dofull + 16;  // [2]
-  const uint32_t bar_dpfull = bar_qdoempty + 16;  // [2] by half
-  const uint32_t bar_pready = bar_dpfull + 16;    // [2] by half
-  const uint32_t bar_dsready = bar_pready + 16;   // [2] by half
-  const uint32_t bar_accfull = bar_dsready + 16;
-  // [half][step parity]; two arrivals each: that half's S^T committed by the tensor core and the step's
-  // LSE / delta rows written by the loader warp, so the compute warps poll one barrier instead of two
-  const uint32_t bar_sfull = bar_accfull + 8;     // [2][2]
-  const uint32_t bar_stempty = bar_sfull + 32;    // [2] by step parity
+  const uint32_t bar_spare0 = bar_qdoempty + 16;
+  const uint32_t bar_dpfull = bar_spare0 + 8;
+  const uint32_t bar_pready = bar_dpfull + 8;
+  const uint32_t bar_dsready = bar_pready + 8;
+  const uint32_t bar_accfull = bar_dsready + 8;
+  // [2] by step parity; two arrivals each: S^T committed by the tensor core and the step's LSE / delta
+  // rows written by the loader warp, so the compute warps poll one barrier instead of two
+  const uint32_t bar_sfull = bar_accfull + 8;
+  const uint32_t bar_stempty = bar_sfull + 16;    // [2]
   uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + kDkdvBars);
 
   const int warp = threadIdx.x >> 5;
@@ -120,13 +115,13 @@ flash_bwd_dkdv_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_cons
       mbar_init(bar_qfull + s * 8, 1);
       mbar_init(bar_dofull + s * 8, 1);
       mbar_init(bar_qdoempty + s * 8, 1);
+      mbar_init(bar_sfull + s * 8, 2);
       mbar_init(bar_stempty + s * 8, kBwdCW);
-      mbar_init(bar_dpfull + s * 8, 1);              // s = half from here on
-      mbar_init(bar_pready + s * 8, kBwdCW / 2);
-      mbar_init(bar_dsready + s * 8, kBwdCW / 2);
-      mbar_init(bar_sfull + (s * 2 + 0) * 8, 2);
-      mbar_init(bar_sfull + (s * 2 + 1) * 8, 2);
     }
+    (void)bar_spare0;
+    mbar_init(bar_dpfull, 1);
+    mbar_init(bar_pready, kBwdCW);
+    mbar_init(bar_dsready, kBwdCW);
     mbar_init(bar_accfull, 1);
     fence_mbar_init();
     tma_prefetch_desc(&tmQ);
@@ -170,10 +165,7 @@ flash_bwd_dkdv_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_cons
         st[kBT + j] = ok ? -p.delta[idx + j] * p.scale : 0.f;  // dS = P * (dP*scale + this)
       }
       __syncwarp();
-      if (lane == 0) {
-        mbar_arrive(bar_sfull + (0 * 2 + s) * 8);
-        mbar_arrive(bar_sfull + (1 * 2 + s) * 8);
-      }
+      if (lane == 0) mbar_arrive(bar_sfull + s * 8);
       if (!mbar_wait_warp(bar_qdoempty + s * 8, ph ^ 1u, p.status)) { aborted = true; break; }
       if (lane == 0) {
         const int col = head * kBD;
@@ -192,21 +184,18 @@ flash_bwd_dkdv_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_cons
     // adds on uniform values); only the elected lane issues tcgen05.mma / tcgen05.commit.
     {
       const uint32_t leader = elect_one();
-      constexpr uint32_t idesc_kh = make_idesc_bf16(kBT, kBT / 2, 0, 0);   // S^T, dP^T of one half (N = 64 queries)
-      constexpr uint32_t idesc_kmn = make_idesc_bf16(kBT, kBD, 0, 1);      // dV, dK (A from TMEM, B MN-major)
+      constexpr uint32_t idesc_kk = make_idesc_bf16(kBT, kBT, 0, 0);   // S^T, dP^T
+      constexpr uint32_t idesc_kmn = make_idesc_bf16(kBT, kBD, 0, 1);  // dV, dK (A from TMEM, B MN-major)
       const uint32_t tS = tmem_base, tdP = tmem_base + 128, tdV = tmem_base + 256, tdK = tmem_base + 384;
       const uint64_t dsc_k = make_sdesc_sw128(sK, 16, 1024), dsc_v = make_sdesc_sw128(sV, 16, 1024);
       const uint64_t dsc_st = make_sdesc_sw128(sStage, 16, 1024);            // K-major view of a stage tile
       const uint64_t dsc_stt = make_sdesc_sw128(sStage, kBT * 128, 1024);    // MN-major view
       constexpr uint64_t kTileU = (uint64_t)(kTileB >> 4);                   // one tile in descriptor units
-      constexpr uint64_t kHalfRowsU = (uint64_t)((kBT / 2) * 128 >> 4);      // query rows 64.. of a K-major tile
-      // D[:, 64 h .. 64 h + 63] = A (K-major, 128 rows) x B^T (K-major, rows 64 h .. 64 h + 63)
-      auto mma_khalf = [&](uint32_t d_tmem, uint64_t a_dsc, uint64_t b_dsc, int h) {
+      auto mma_kmajor = [&](uint32_t d_tmem, uint64_t a_dsc, uint64_t b_dsc) {
 #pragma unroll
         for (int ks = 0; ks < kBD / 16; ++ks) {
           const uint64_t off = (uint64_t)(((ks / 4) * (kBT * 128) + (ks % 4) * 32) >> 4);
-          umma_ss_p(d_tmem + h * (kBT / 2), a_dsc + off, b_dsc + off + (uint64_t)h * kHalfRowsU, idesc_kh,
-                    ks > 0 ? 1u : 0u, leader);
+          umma_ss_p(d_tmem, a_dsc + off, b_dsc + off, idesc_kk, ks > 0 ? 1u : 0u, leader);
         }
       };
       do {
@@ -214,63 +203,45 @@ flash_bwd_dkdv_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_cons
         if (!mbar_wait(bar_kv, 0, p.status)) { aborted = true; break; }
         if (!mbar_wait(bar_qfull, 0, p.status)) { aborted = true; break; }
         tc_fence_after();
-        for (int h = 0; h < 2; ++h) {
-          mma_khalf(tS, dsc_k, dsc_st, h);
-          umma_commit_p(bar_sfull + (h * 2 + 0) * 8, leader);   // step 0
-        }
+        mma_kmajor(tS, dsc_k, dsc_st);
+        umma_commit_p(bar_sfull, leader);   // step 0
         if (!mbar_wait(bar_dofull, 0, p.status)) { aborted = true; break; }
         tc_fence_after();
-        for (int h = 0; h < 2; ++h) {
-          mma_khalf(tdP, dsc_v, dsc_st + kTileU, h);
-          umma_commit_p(bar_dpfull + h * 8, leader);
-        }
+        mma_kmajor(tdP, dsc_v, dsc_st + kTileU);
+        umma_commit_p(bar_dpfull, leader);
         for (int i = 0; i < n_iter; ++i) {
           const int s = i & 1, s1 = s ^ 1;
           const uint32_t par = (uint32_t)i & 1u;
           // stage s: Q at tile 2s, dO at tile 2s + 1
           const uint64_t q_s = dsc_stt + (uint64_t)(2 * s) * kTileU, do_s = q_s + kTileU;
           const uint64_t q_n = dsc_st + (uint64_t)(2 * s1) * kTileU, do_n = q_n + kTileU;
-          for (int h = 0; h < 2 && !aborted; ++h) {
-            // dV += P^T dO over this half's queries: A = P^T from TMEM, B = dO viewed [d, q] (MN-major)
-            if (!mbar_wait(bar_pready + h * 8, par, p.status)) { aborted = true; break; }
-            tc_fence_after();
+          // dV += P^T dO : A = P^T from TMEM, B = dO viewed [d, q] (MN-major)
+          if (!mbar_wait(bar_pready, par, p.status)) { aborted = true; break; }
+          tc_fence_after();
 #pragma unroll
-            for (int k4 = 0; k4 < kBT / 32; ++k4) {
-              const int kk = h * (kBT / 32) + k4;
-              umma_ts_p(tdV, tS + (kk / 2) * 32 + (kk % 2) * 8, do_s + (uint64_t)((kk * 2048) >> 4), idesc_kmn,
-                        (i > 0 || kk > 0) ? 1u : 0u, leader);
-            }
-            if (i + 1 < n_iter) {
-              if (h == 0) {
-                if (!mbar_wait(bar_qfull + s1 * 8, (uint32_t)((i + 1) >> 1) & 1u, p.status)) { aborted = true; break; }
-                tc_fence_after();
-              }
-              mma_khalf(tS, dsc_k, q_n, h);        // overwrites this half's P^T, already consumed by dV above
-              umma_commit_p(bar_sfull + (h * 2 + s1) * 8, leader);
-            }
-          }
-          if (aborted) break;
-          for (int h = 0; h < 2 && !aborted; ++h) {
-            // dK += dS^T Q over this half's queries: A = dS^T from TMEM, B = Q viewed [d, q] (MN-major)
-            if (!mbar_wait(bar_dsready + h * 8, par, p.status)) { aborted = true; break; }
+          for (int kk = 0; kk < kBT / 16; ++kk)
+            umma_ts_p(tdV, tS + (kk / 2) * 32 + (kk % 2) * 8, do_s + (uint64_t)((kk * 2048) >> 4), idesc_kmn,
+                      (i > 0 || kk > 0) ? 1u : 0u, leader);
+          if (i + 1 < n_iter) {
+            if (!mbar_wait(bar_qfull + s1 * 8, (uint32_t)((i + 1) >> 1) & 1u, p.status)) { aborted = true; break; }
             tc_fence_after();
-#pragma unroll
-            for (int k4 = 0; k4 < kBT / 32; ++k4) {
-              const int kk = h * (kBT / 32) + k4;
-              umma_ts_p(tdK, tdP + (kk / 2) * 32 + (kk % 2) * 8, q_s + (uint64_t)((kk * 2048) >> 4), idesc_kmn,
-                        (i > 0 || kk > 0) ? 1u : 0u, leader);
-            }
-            if (h == 1) umma_commit_p(bar_qdoempty + s * 8, leader);
-            if (i + 1 < n_iter) {
-              if (h == 0) {
-                if (!mbar_wait(bar_dofull + s1 * 8, (uint32_t)((i + 1) >> 1) & 1u, p.status)) { aborted = true; break; }
-                tc_fence_after();
-              }
-              mma_khalf(tdP, dsc_v, do_n, h);
-              umma_commit_p(bar_dpfull + h * 8, leader);
-            }
+            mma_kmajor(tS, dsc_k, q_n);
+            umma_commit_p(bar_sfull + s1 * 8, leader);
           }
-          if (aborted) break;
+          // dK += dS^T Q : A = dS^T from TMEM, B = Q viewed [d, q] (MN-major)
+          if (!mbar_wait(bar_dsready, par, p.status)) { aborted = true; break; }
+          tc_fence_after();
+#pragma unroll
+          for (int kk = 0; kk < kBT / 16; ++kk)
+            umma_ts_p(tdK, tdP + (kk / 2) * 32 + (kk % 2) * 8, q_s + (uint64_t)((kk * 2048) >> 4), idesc_kmn,
+                      (i > 0 || kk > 0) ? 1u : 0u, leader);
+          umma_commit_p(bar_qdoempty + s * 8, leader);
+          if (i + 1 < n_iter) {
+            if (!mbar_wait(bar_dofull + s1 * 8, (uint32_t)((i + 1) >> 1) & 1u, p.status)) { aborted = true; break; }
+            tc_fence_after();
+            mma_kmajor(tdP, dsc_v, do_n);
+            umma_commit_p(bar_dpfull, leader);
+          }
         }
         if (!aborted) umma_commit_p(bar_accfull, leader);
       } while (false);
@@ -279,7 +250,6 @@ flash_bwd_dkdv_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_cons
   } else {
     // ------------------------------ compute warps ------------------------------
     const int cw = warp >> 2;                    // query columns cw * kBwdCols .. + kBwdCols - 1
-    const int half = cw >> 1;                    // queries 0-63 or 64-127: own barriers, own slice of every product
     const int qd = warp & 3;
     const int r = qd * 32 + lane;                // TMEM lane = key row of the tile
     const uint32_t lane_base = (uint32_t)(qd * 32) << 16;
@@ -293,7 +263,7 @@ flash_bwd_dkdv_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_cons
       const float* st = s_stats + (i & 1) * 256;
       float pf[kBwdCols];
       // ---- P^T = exp2(S^T * c - lse2), masked ----
-      if (!mbar_wait_warp(bar_sfull + (half * 2 + (i & 1)) * 8, (uint32_t)(i >> 1) & 1u, p.status)) { aborted = true; break; }
+      if (!mbar_wait_warp(bar_sfull + (i & 1) * 8, (uint32_t)(i >> 1) & 1u, p.status)) { aborted = true; break; }
       tc_fence_after();
       {
         uint32_t sv[32];
@@ -330,9 +300,9 @@ flash_bwd_dkdv_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_cons
       }
       tc_fence_before();
       __syncwarp();
-      if (lane == 0) mbar_arrive(bar_pready + half * 8);
+      if (lane == 0) mbar_arrive(bar_pready);
       // ---- dS^T = P^T o (dP^T - delta) * scale, written over dP^T as bf16 ----
-      if (!mbar_wait_warp(bar_dpfull + half * 8, par, p.status)) { aborted = true; break; }
+      if (!mbar_wait_warp(bar_dpfull, par, p.status)) { aborted = true; break; }
       tc_fence_after();
       {
         uint32_t dv[32];
@@ -358,7 +328,7 @@ flash_bwd_dkdv_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_cons
       tc_fence_before();
       __syncwarp();
       if (lane == 0) {
-        mbar_arrive(bar_dsready + half * 8);
+        mbar_arrive(bar_dsready);
         mbar_arrive(bar_stempty + (i & 1) * 8);
       }
     }
