@@ -598,6 +598,16 @@ extern "C" int dca_gemm_bf16_tp(const void* A, const void* B, void* C, int M, in
                    a_peers, n_a_peers, a_rows_per_peer, c_peers, n_c_peers, c_rows_per_peer, status, stream);
 }
 
+// FC1 of the MLP under tensor + sequence parallelism: the all-gather of the activation is fused into the A load
+// (a_peers as in dca_gemm_bf16_tp) and SwiGLU runs in the epilogue (epi = 1 of dca_gemm_bf16: N = 2F,
+// C[M, F] = silu(gate) * up, `preact` (may be null) receives the bf16 (gate | up) as [M, 2F]).
+extern "C" int dca_gemm_swiglu_tp(const void* B, void* C, int M, int N, int K, long lda, long ldb, long ldc,
+                                  void* preact, long ld_preact, const void* const* a_peers, int n_a_peers,
+                                  long a_rows_per_peer, unsigned int* status, void* stream) {
+  return gemm_impl(nullptr, B, C, M, N, K, lda, ldb, ldc, 0, 0, 0, 0, dca::gemm::EPI_SWIGLU, preact, ld_preact,
+                   nullptr, 0, a_peers, n_a_peers, a_rows_per_peer, nullptr, 0, 0, status, stream);
+}
+
 // QKV projection with RoPE and the core-attention dispatch in the epilogue (head_dim 128).
 // N = (heads_q + 2 * heads_kv) * 128, Q heads first, then K, then V. `pos` [M] int32, `table` fp32
 // [max_pos, 128] (cos | sin); a position outside [0, max_pos) is clamped and sets the status word. C (may be null when destinations are given) receives the rotated rows;

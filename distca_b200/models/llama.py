@@ -346,11 +346,22 @@ class LlamaLayer:
             else:
                 h = self.tp.reduce_scatter_rows(gemm.linear_fwd(attn_out, self.w["wo"]))
                 ew.add_(h, x)
-        with timers.phase("norm"):
-            n2, rstd2 = ew.rmsnorm_fwd(h, self.w["ln2"], self.cfg.norm_eps)
-        n2f = self.tp.all_gather_rows(n2)
+        if fused is not None:
+            # FC1: the normalised shard goes into the peer arena, the GEMM reads every rank's shard tile by tile
+            # (all-gather fused into the operand load) and applies SwiGLU in its epilogue
+            with timers.phase("norm"):
+                buf = fused.stage_buffer(h.shape[0], h.shape[1])
+                _, rstd2 = ew.rmsnorm_fwd(h, self.w["ln2"], self.cfg.norm_eps, out=buf)
+            with timers.phase("gemm_fwd"):
+                act, pre = fused.ag_linear_swiglu(buf, self.w["w13"], keep_preact=keep)
+            n2f = buf.clone() if keep else None    # local shard only; gathered again for the weight gradient
+        else:
+            with timers.phase("norm"):
+                n2, rstd2 = ew.rmsnorm_fwd(h, self.w["ln2"], self.cfg.norm_eps)
+            n2f = self.tp.all_gather_rows(n2)
+            with timers.phase("gemm_fwd"):
+                act, pre = gemm.linear_swiglu_fwd(n2f, self.w["w13"], keep_preact=keep)
         with timers.phase("gemm_fwd"):
-            act, pre = gemm.linear_swiglu_fwd(n2f, self.w["w13"], keep_preact=keep)
             if self.tp.size == 1:
                 y = gemm.linear_fwd(act, self.w["w2"], residual=h)
             elif fused is not None:
@@ -444,6 +455,9 @@ class LlamaLayer:
     # ---- backward pieces ----
     def bwd_post_ca(self, c: LayerCtx, dy):
         """dy -> (dattn, dh). Accumulates dW2, dW13, dln2, dWo."""
+        fused = getattr(self.tp, "fused", None)
+        if fused is not None and dy.shape[0] % 128 == 0:
+            return self._bwd_post_ca_fused(c, dy, fused)
         dyf = self.tp.all_gather_rows(dy)
         with timers.phase("gemm_bwd"):
             dact = gemm.linear_dgrad(dyf, self.w["w2"])
@@ -452,9 +466,11 @@ class LlamaLayer:
         with timers.phase("swiglu_bwd"):
             dpre = ew.swiglu_bwd(c.pre, dact, inplace=True)
         del dact
+        n2f = c.n2 if c.n2.shape[0] == dpre.shape[0] else self.tp.all_gather_rows(c.n2)
         with timers.phase("gemm_bwd"):
             dn2 = self.tp.reduce_scatter_rows(gemm.linear_dgrad(dpre, self.w["w13"]))
-            gemm.linear_wgrad(dpre, c.n2, out=self.g["w13"], accumulate=True)
+            gemm.linear_wgrad(dpre, n2f, out=self.g["w13"], accumulate=True)
+        del n2f
         c.pre = c.n2 = None
         del dpre
         with timers.phase("norm_bwd"):
@@ -467,16 +483,65 @@ class LlamaLayer:
         c.attn_out = c.h = None
         return dattn, dh
 
+    def _bwd_post_ca_fused(self, c: LayerCtx, dy, fused):
+        """Tensor + sequence parallel backward of the post-attention half without NCCL: the data-gradient GEMMs
+        read the peers' shards in their operand loads (all-gather -> GEMM) or scatter their rows to the owners
+        in their epilogues (GEMM -> reduce-scatter); the weight-gradient GEMMs need the token dimension as their
+        reduction dimension, so their sharded operand is gathered by peer stores first (``all_gather_rows``)."""
+        rows, H = dy.shape
+        with timers.phase("gemm_bwd"):
+            buf = fused.stage_buffer(rows, H)
+            buf.copy_(dy)
+            dact = fused.ag_linear(buf, self.w["w2"], transposed_weight=True)            # all_gather(dy) @ W2
+            dyf = fused.all_gather_rows(dy)
+            gemm.linear_wgrad(dyf, c.act, out=self.g["w2"], accumulate=True)
+            fused.release_gather()
+        c.act = None
+        with timers.phase("swiglu_bwd"):
+            dpre = ew.swiglu_bwd(c.pre, dact, inplace=True)
+        del dact
+        with timers.phase("gemm_bwd"):
+            dn2 = fused.linear_rs(dpre, self.w["w13"], transposed_weight=True)          # reduce_scatter(dpre @ W13)
+            n2f = c.n2 if c.n2.shape[0] == dpre.shape[0] else fused.all_gather_rows(c.n2)
+            gemm.linear_wgrad(dpre, n2f, out=self.g["w13"], accumulate=True)
+            if c.n2.shape[0] != dpre.shape[0]:
+                fused.release_gather()
+        del n2f
+        c.pre = c.n2 = None
+        del dpre
+        with timers.phase("norm_bwd"):
+            dh = ew.rmsnorm_bwd(c.h, self.w["ln2"], c.rstd2, dn2, self.g["ln2"], dres=dy)
+        del dn2
+        with timers.phase("gemm_bwd"):
+            buf = fused.stage_buffer(rows, H)
+            buf.copy_(dh)
+            dattn = fused.ag_linear(buf, self.w["wo"], transposed_weight=True)           # all_gather(dh) @ Wo
+            dhf = fused.all_gather_rows(dh)
+            gemm.linear_wgrad(dhf, c.attn_out, out=self.g["wo"], accumulate=True)
+            fused.release_gather()
+        c.attn_out = c.h = None
+        return dattn, dh
+
     def bwd_pre_ca(self, c: LayerCtx, dqkv, dh, pos, rope_table):
         """(dqkv, dh) -> dx. Accumulates dWqkv, dln1."""
         with timers.phase("rope"):
             ew.rope_(dqkv, pos, rope_table, self.hq, self.hkv, self.cfg.head_dim, backward=True)
         if self.cfg.qkv_bias:
             self.g["bqkv"] += dqkv.float().sum(0).to(self.g["bqkv"].dtype)
-        n1f = c.n1 if c.n1.shape[0] == dqkv.shape[0] else self.tp.all_gather_rows(c.n1)
-        with timers.phase("gemm_bwd"):
-            dn1 = self.tp.reduce_scatter_rows(gemm.linear_dgrad(dqkv, self.w["wqkv"]))
-            gemm.linear_wgrad(dqkv, n1f, out=self.g["wqkv"], accumulate=True)
+        fused = getattr(self.tp, "fused", None)
+        if fused is not None and dqkv.is_contiguous() and dh.shape[0] % 128 == 0:
+            with timers.phase("gemm_bwd"):
+                dn1 = fused.linear_rs(dqkv, self.w["wqkv"], transposed_weight=True)     # reduce_scatter(dqkv @ Wqkv)
+                gathered = c.n1.shape[0] != dqkv.shape[0]
+                n1f = fused.all_gather_rows(c.n1) if gathered else c.n1
+                gemm.linear_wgrad(dqkv, n1f, out=self.g["wqkv"], accumulate=True)
+                if gathered:
+                    fused.release_gather()
+        else:
+            n1f = c.n1 if c.n1.shape[0] == dqkv.shape[0] else self.tp.all_gather_rows(c.n1)
+            with timers.phase("gemm_bwd"):
+                dn1 = self.tp.reduce_scatter_rows(gemm.linear_dgrad(dqkv, self.w["wqkv"]))
+                gemm.linear_wgrad(dqkv, n1f, out=self.g["wqkv"], accumulate=True)
         del n1f
         c.n1 = None
         with timers.phase("norm_bwd"):

@@ -242,6 +242,7 @@ class CadRuntime:
     # ------------------------------------------------------------------------------------------
     # measured-speed feedback into the planner
     _FWD_SHARE = 0.23      # forward share of the cost model's forward + backward milliseconds
+    MIN_FEEDBACK_MS = 20.0 # mean attention time per step below which the measurements are not fed back
 
     def _timed_attention(self, share: float):
         """Context manager: CUDA events around one attention call (read back at the end of the step)."""
@@ -304,16 +305,18 @@ class CadRuntime:
         if (allv[:, :2] <= 0).any():
             return                       # a server without work this step: keep the current shares
         self.last_measured = allv
+        self.plan_stats["attention_ms_per_server"] = [round(float(v), 2) for v in allv[:, 0]]
+        self.plan_stats["attention_time_imbalance"] = float(allv[:, 0].max() / allv[:, 0].mean())
+        if allv[:, 0].mean() < self.MIN_FEEDBACK_MS:
+            return                       # a step this short measures launch overheads, not the servers' speed
         share = self.feedback_shares(allv[:, 0], allv[:, 1], allv[:, 2], wait_gain)
-        speed = share
-        if self.speed is not None:
-            speed = smoothing * speed + (1.0 - smoothing) * self.speed
+        prev = self.speed if self.speed is not None else np.ones(self.W)
+        speed = smoothing * share + (1.0 - smoothing) * prev
+        speed = np.clip(speed, prev * 0.95, prev * 1.05)          # at most 5 % per step: one odd step cannot swing the plan
         self.speed = speed / speed.mean()
         self.plan_stats["idle_ms_per_server"] = [round(float(v), 2) for v in allv[:, 2]]
         self._pending_speed = self.speed.tolist()
         self.plan_stats["speed"] = [round(float(v), 4) for v in self.speed]
-        self.plan_stats["attention_ms_per_server"] = [round(float(v), 2) for v in allv[:, 0]]
-        self.plan_stats["attention_time_imbalance"] = float(allv[:, 0].max() / allv[:, 0].mean())
     # ------------------------------------------------------------------------------------------
     # server halves (every rank of the group runs them once per layer and direction)
     @staticmethod

@@ -24,6 +24,7 @@ class TensorParallel:
         self.device = torch.device(device)
         self.on_gpu = self.device.type == "cuda"
         self.fused = None   # PeerCollectives: all-gather / reduce-scatter fused into the GEMMs
+        self.nccl_row_collectives = 0   # all_gather_rows / reduce_scatter_rows calls that went to NCCL (diagnostic)
         self.use_p2p = use_p2p and self.on_gpu
         self._max_cols = max_cols
         if self.use_p2p and max_rows_local > 0:
@@ -43,11 +44,13 @@ class TensorParallel:
         self.fused = PeerCollectives(self.group, self.size, self.rank, self.device, rows_local, self._max_cols)
 
     def all_gather_rows(self, x: torch.Tensor) -> torch.Tensor:
+        self.nccl_row_collectives += 1
         out = torch.empty((x.shape[0] * self.size,) + tuple(x.shape[1:]), dtype=x.dtype, device=x.device)
         dist.all_gather_into_tensor(out, x.contiguous(), group=self.group)
         return out
 
     def reduce_scatter_rows(self, x: torch.Tensor) -> torch.Tensor:
+        self.nccl_row_collectives += 1
         n = x.shape[0] // self.size
         if self.on_gpu:
             out = torch.empty((n,) + tuple(x.shape[1:]), dtype=x.dtype, device=x.device)

@@ -24,7 +24,7 @@ from ..ops import _lib
 from ..ops import elementwise as ew
 from .p2p import PeerArena, SignalBoard, sum_slots
 
-SIG_STAGED, SIG_READ, SIG_PARTIAL, SIG_SUMMED = 0, 1, 2, 3
+SIG_STAGED, SIG_READ, SIG_PARTIAL, SIG_SUMMED, SIG_GIN, SIG_GDONE = 0, 1, 2, 3, 4, 5
 
 
 class PeerCollectives:
@@ -34,11 +34,14 @@ class PeerCollectives:
         self.device = torch.device(device)
         self.max_rows, self.max_cols = max_rows_local, max_cols
         shard = max_rows_local * max_cols * 2
-        self.arena = PeerArena(shard * (1 + size) + (1 << 20), group, device)
-        self.sig = SignalBoard(self.arena, 4)
+        self.arena = PeerArena(shard * (1 + 2 * size) + (1 << 20), group, device)
+        self.sig = SignalBoard(self.arena, 6)
         self.off_x = self.arena.alloc(shard, align=4096)
         self.off_slots = self.arena.alloc(shard * size, align=4096)
+        self.off_gather = self.arena.alloc(shard * size, align=4096)
         self.x_addrs = [self.arena.addr(p, self.off_x) for p in range(size)]
+        self.gather_tbl = torch.tensor([self.arena.addr(p, self.off_gather) for p in range(size)],
+                                       dtype=torch.int64, device=self.device)
         self._valid = None
 
     # ------------------------------------------------------------------------------------------
@@ -50,11 +53,14 @@ class PeerCollectives:
         return self.arena.view(self.off_x, (rows, cols), torch.bfloat16)
 
     def ag_linear(self, x_staged: torch.Tensor, w: torch.Tensor, out: torch.Tensor | None = None,
-                  rope: dict | None = None) -> torch.Tensor:
+                  rope: dict | None = None, transposed_weight: bool = False) -> torch.Tensor:
         """``concat_over_ranks(x_staged) @ w.T`` with the all-gather fused into the GEMM's operand load.
-        ``x_staged`` must be the tensor returned by :meth:`stage_buffer` (already filled)."""
+        ``x_staged`` must be the tensor returned by :meth:`stage_buffer` (already filled).
+        ``transposed_weight``: ``concat(...) @ w`` instead (``w`` [K, N]: the data-gradient twin of a
+        row-parallel linear, e.g. ``dattn = all_gather(dh) @ W_o``)."""
         rows, K = x_staged.shape
-        N = w.shape[0]
+        N = w.shape[1] if transposed_weight else w.shape[0]
+        assert rope is None or not transposed_weight
         T = rows * self.size
         if out is None:
             out = torch.empty(T, N, dtype=torch.bfloat16, device=self.device)
@@ -69,17 +75,39 @@ class PeerCollectives:
             return out
         rc = _lib.lib().dca_gemm_bf16_tp(
             None, _lib.ptr(w), _lib.ptr(out), _lib.c_int(T), _lib.c_int(N), _lib.c_int(K), _lib.c_long(K),
-            _lib.c_long(w.stride(0)), _lib.c_long(out.stride(0)), _lib.c_int(0), a_peers, _lib.c_int(self.size),
-            _lib.c_long(rows), None, _lib.c_int(0), _lib.c_long(0), _lib.ptr(_lib.status_word(self.device)),
-            _lib.stream_ptr())
+            _lib.c_long(w.stride(0)), _lib.c_long(out.stride(0)), _lib.c_int(1 if transposed_weight else 0), a_peers,
+            _lib.c_int(self.size), _lib.c_long(rows), None, _lib.c_int(0), _lib.c_long(0),
+            _lib.ptr(_lib.status_word(self.device)), _lib.stream_ptr())
         _lib.check_rc(rc, "gemm_ag")
         self.sig.signal(SIG_READ)
         return out
 
-    def linear_rs(self, x: torch.Tensor, w: torch.Tensor, residual: torch.Tensor | None = None) -> torch.Tensor:
-        """``reduce_scatter_rows(x @ w.T) (+ residual)`` with the scatter fused into the GEMM epilogue."""
+    def ag_linear_swiglu(self, x_staged: torch.Tensor, w_gate_up: torch.Tensor, keep_preact: bool = False):
+        """FC1: ``silu(gate) * up`` of ``concat_over_ranks(x_staged) @ w_gate_up.T`` with the all-gather fused
+        into the GEMM's operand load and SwiGLU in its epilogue. Returns ``(act, pre or None)``."""
+        rows, K = x_staged.shape
+        F2 = w_gate_up.shape[0]
+        T = rows * self.size
+        act = torch.empty(T, F2 // 2, dtype=torch.bfloat16, device=self.device)
+        pre = torch.empty(T, F2, dtype=torch.bfloat16, device=self.device) if keep_preact else None
+        self.sig.signal(SIG_STAGED)
+        self.sig.wait(SIG_STAGED)
+        a_peers = (ctypes.c_void_p * self.size)(*self.x_addrs)
+        rc = _lib.lib().dca_gemm_swiglu_tp(
+            _lib.ptr(w_gate_up), _lib.ptr(act), _lib.c_int(T), _lib.c_int(F2), _lib.c_int(K), _lib.c_long(K),
+            _lib.c_long(w_gate_up.stride(0)), _lib.c_long(F2 // 2), _lib.ptr(pre), _lib.c_long(F2), a_peers,
+            _lib.c_int(self.size), _lib.c_long(rows), _lib.ptr(_lib.status_word(self.device)), _lib.stream_ptr())
+        _lib.check_rc(rc, "gemm_ag_swiglu")
+        self.sig.signal(SIG_READ)
+        return act, pre
+
+    def linear_rs(self, x: torch.Tensor, w: torch.Tensor, residual: torch.Tensor | None = None,
+                  transposed_weight: bool = False) -> torch.Tensor:
+        """``reduce_scatter_rows(x @ w.T) (+ residual)`` with the scatter fused into the GEMM epilogue.
+        ``transposed_weight``: ``x @ w`` instead (``w`` [K, N]: the data-gradient twin of a column-parallel
+        linear, e.g. ``dn = reduce_scatter(dqkv @ W_qkv)``)."""
         T, K = x.shape
-        N = w.shape[0]
+        N = w.shape[1] if transposed_weight else w.shape[0]
         rows = T // self.size
         assert rows <= self.max_rows and N <= self.max_cols
         self.sig.wait(SIG_SUMMED)  # every owner has consumed the previous partial rows
@@ -88,8 +116,9 @@ class PeerCollectives:
                                                  for p in range(self.size)])
         rc = _lib.lib().dca_gemm_bf16_tp(
             _lib.ptr(x), _lib.ptr(w), None, _lib.c_int(T), _lib.c_int(N), _lib.c_int(K), _lib.c_long(x.stride(0)),
-            _lib.c_long(w.stride(0)), _lib.c_long(N), _lib.c_int(0), None, _lib.c_int(0), _lib.c_long(0), c_peers,
-            _lib.c_int(self.size), _lib.c_long(rows), _lib.ptr(_lib.status_word(self.device)), _lib.stream_ptr())
+            _lib.c_long(w.stride(0)), _lib.c_long(N), _lib.c_int(1 if transposed_weight else 0), None, _lib.c_int(0),
+            _lib.c_long(0), c_peers, _lib.c_int(self.size), _lib.c_long(rows), _lib.ptr(_lib.status_word(self.device)),
+            _lib.stream_ptr())
         _lib.check_rc(rc, "gemm_rs")
         self.sig.signal(SIG_PARTIAL)
         self.sig.wait(SIG_PARTIAL)
@@ -103,6 +132,29 @@ class PeerCollectives:
             ew.add_(out, residual)
         self.sig.signal(SIG_SUMMED)
         return out
+
+    # ------------------------------------------------------------------------------------------
+    def all_gather_rows(self, x: torch.Tensor) -> torch.Tensor:
+        """All-gather of row shards by peer stores (this repository's push kernel over NVLink, no NCCL): every
+        rank stores its [rows, cols] shard into every peer's gather buffer. Returns the gathered
+        [size * rows, cols] view of THIS rank's gather buffer; call :meth:`release_gather` once the kernels that
+        read it are queued (the next gather waits until every peer has released)."""
+        rows, cols = x.shape
+        assert rows <= self.max_rows and cols <= self.max_cols and x.dtype == torch.bfloat16
+        x = x.contiguous()
+        nbytes = rows * cols * 2
+        self.sig.wait(SIG_GDONE)          # every peer has finished reading the previous gather
+        mine = self.arena.view(self.off_gather + self.rank * nbytes, (rows, cols), torch.bfloat16)
+        mine.copy_(x)
+        rc = _lib.lib().dca_push_shard(_lib.ptr(x), _lib.ptr(self.gather_tbl), _lib.c_int(self.size), _lib.c_int(self.rank),
+                                       _lib.c_long(self.rank * nbytes), _lib.c_long(nbytes), _lib.stream_ptr())
+        _lib.check_rc(rc, "push_shard")
+        self.sig.signal(SIG_GIN)
+        self.sig.wait(SIG_GIN)
+        return self.arena.view(self.off_gather, (self.size * rows, cols), torch.bfloat16)
+
+    def release_gather(self) -> None:
+        self.sig.signal(SIG_GDONE)
 
     def close(self) -> None:
         self.arena.close()

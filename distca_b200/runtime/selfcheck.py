@@ -162,7 +162,8 @@ def check_tp(a) -> int:
         src = BatchSource(cfg, par, a.tokens, a.dist, seed=a.seed)
         losses = [tr.train_step(src.next(tr.dp_rank)) for _ in range(a.steps)]
         tr.check_device_status()
-        out[transport] = (losses, tr.model.store.grad.float().clone(), tr.model.tp.fused is not None)
+        out[transport] = (losses, tr.model.store.grad.float().clone(), tr.model.tp.fused is not None,
+                          tr.model.tp.nccl_row_collectives // a.steps)
         if tr.model.tp.fused is not None:
             tr.model.tp.fused.close()
         tr.close()
@@ -175,7 +176,8 @@ def check_tp(a) -> int:
     dist.all_reduce(flags, op=dist.ReduceOp.MIN)
     if rank == 0:
         print(json.dumps({"check": "tp", "ok": bool(flags.item()), "loss_nccl": out["nccl"][0], "loss_p2p": out["p2p"][0],
-                          "fused": out["p2p"][2] and not out["nccl"][2], "grad_cosine": cos, "grad_max_err": (g0 - g1).abs().max().item()}))
+                          "fused": out["p2p"][2] and not out["nccl"][2],
+                          "nccl_row_collectives_per_step": {"nccl": out["nccl"][3], "p2p": out["p2p"][3]}, "grad_cosine": cos, "grad_max_err": (g0 - g1).abs().max().item()}))
     dist.barrier()
     return 0 if flags.item() else 1
 

@@ -67,6 +67,27 @@ def test_gemm_with_reduce_scatter_in_the_epilogue(peers, rows, N, K):
         assert _rel(got, ref) < 2e-2
 
 
+def test_swiglu_gemm_reads_shards_of_several_peers():
+    """FC1 with the all-gather in the operand load and SwiGLU in the epilogue."""
+    torch.manual_seed(5)
+    peers, rows, F, K = 4, 128, 384, 256
+    T = peers * rows
+    shards = [_bf(rows, K) for _ in range(peers)]
+    w = _bf(2 * F, K, scale=0.1)
+    act = torch.empty(T, F, dtype=torch.bfloat16, device="cuda")
+    pre = torch.empty(T, 2 * F, dtype=torch.bfloat16, device="cuda")
+    ap = (ctypes.c_void_p * peers)(*[t.data_ptr() for t in shards])
+    rc = _lib.lib().dca_gemm_swiglu_tp(_lib.ptr(w), _lib.ptr(act), _lib.c_int(T), _lib.c_int(2 * F), _lib.c_int(K),
+                                       _lib.c_long(K), _lib.c_long(w.stride(0)), _lib.c_long(F), _lib.ptr(pre),
+                                       _lib.c_long(2 * F), ap, _lib.c_int(peers), _lib.c_long(rows),
+                                       _lib.ptr(_lib.status_word("cuda")), _lib.stream_ptr())
+    _lib.check_rc(rc, "gemm_ag_swiglu")
+    _lib.check_status()
+    ref_pre = torch.cat(shards).float() @ w.float().t()
+    ref_act = torch.nn.functional.silu(ref_pre[:, :F]) * ref_pre[:, F:]
+    assert _rel(pre, ref_pre) < 1e-2 and _rel(act, ref_act) < 2e-2
+
+
 def test_qkv_rope_gemm_reads_shards_of_several_peers():
     torch.manual_seed(2)
     peers, rows, Hq, Hkv, D, K = 4, 128, 4, 2, 128, 256
