@@ -334,7 +334,9 @@ class LlamaLayer:
                 core_attn.apply_rope(qkv, pos, rope_table)
         return qkv, n1f, rstd1
 
-    def post_ca(self, x, attn_out, keep: bool):
+    def post_ca(self, x, attn_out, keep: bool, need_output: bool = True):
+        """``need_output=False`` (the recompute pass of backward): the layer's output is not needed again (it is
+        the next layer's saved input), so the FC2 GEMM is skipped."""
         fused = getattr(self.tp, "fused", None)
         if fused is not None and x.shape[0] % 128 != 0:
             fused = None
@@ -362,7 +364,9 @@ class LlamaLayer:
             with timers.phase("gemm_fwd"):
                 act, pre = gemm.linear_swiglu_fwd(n2f, self.w["w13"], keep_preact=keep)
         with timers.phase("gemm_fwd"):
-            if self.tp.size == 1:
+            if not need_output:
+                y = None
+            elif self.tp.size == 1:
                 y = gemm.linear_fwd(act, self.w["w2"], residual=h)
             elif fused is not None:
                 y = fused.linear_rs(act, self.w["w2"], residual=h)
@@ -371,10 +375,12 @@ class LlamaLayer:
                 ew.add_(y, h)
         return y, h, rstd2, n2f, pre, act
 
-    def forward(self, x, pos, rope_table, core_attn, keep: bool, attn_store=None, saved_attn=None):
+    def forward(self, x, pos, rope_table, core_attn, keep: bool, attn_store=None, saved_attn=None,
+                need_output: bool = True):
         """``attn_store`` (first forward under ``keep_attn``): the core-attention output is saved there and
         the attention module keeps the softmax statistics. ``saved_attn`` (recompute under ``keep_attn``):
-        that saved output; core attention is not run again."""
+        that saved output; core attention is not run again. ``need_output=False``: recompute pass, only the
+        context for backward is wanted."""
         qkv, n1f, rstd1 = self.pre_ca(x, pos, rope_table, core_attn)
         with timers.phase("attn_fwd"):
             if saved_attn is not None:
@@ -383,12 +389,12 @@ class LlamaLayer:
                 attn_out, ca_ctx = core_attn.forward(qkv, self.index)
                 if attn_store is not None and not keep:
                     attn_store.save(self.index, core_attn.pack_saved(attn_out, ca_ctx), clone=False)
-        y, h, rstd2, n2f, pre, act = self.post_ca(x, attn_out, keep)
+        y, h, rstd2, n2f, pre, act = self.post_ca(x, attn_out, keep, need_output)
         if not keep:
             return y, None
         return y, LayerCtx(x, rstd1, n1f, ca_ctx, attn_out, h, rstd2, n2f, pre, act)
 
-    def forward_nano(self, xs, poss, rope_table, cas, keep: bool, stores=None, saved=None):
+    def forward_nano(self, xs, poss, rope_table, cas, keep: bool, stores=None, saved=None, need_output: bool = True):
         """Forward of this layer for several nano-batches, ping-pong order: every nano-batch runs
         pre-CA (which dispatches its Q/K/V), then every attention server call is issued, and only then
         does each nano-batch collect its attention output and run post-CA, so one nano-batch's
@@ -422,7 +428,7 @@ class LlamaLayer:
                 attn_out, ca_ctx = cas[k].restore(qkv, saved[k], self.index)
             elif saving:
                 stores[k].save(self.index, cas[k].pack_saved(attn_out, ca_ctx), clone=False)
-            y, h, rstd2, n2f, prea, act = self.post_ca(xs[k], attn_out, keep)
+            y, h, rstd2, n2f, prea, act = self.post_ca(xs[k], attn_out, keep, need_output)
             outs.append((y, LayerCtx(xs[k], rstd1, n1f, ca_ctx, attn_out, h, rstd2, n2f, prea, act) if keep else None))
         return outs
 
@@ -783,7 +789,8 @@ class LlamaModel:
                     saved = store.load(layer.index)
                     store.prefetch(self.layers[i - 1].index if i > 0 else -1)
                 with timers.layer("recompute", layer.index):
-                    _, ctx = layer.forward(inputs[i], batch.pos, self.rope_table, core_attn, True, saved_attn=saved)
+                    _, ctx = layer.forward(inputs[i], batch.pos, self.rope_table, core_attn, True, saved_attn=saved,
+                                           need_output=False)
                 del saved
             inputs[i] = None
             with timers.layer("bwd", layer.index):
@@ -837,7 +844,8 @@ class LlamaModel:
                             if inputs[i][k] is not None:
                                 st.prefetch(self.layers[i - 1].index)
                 with timers.layer("recompute", layer.index):
-                    outs = layer.forward_nano(inputs[i], poss, self.rope_table, cas, True, saved=saved)
+                    outs = layer.forward_nano(inputs[i], poss, self.rope_table, cas, True, saved=saved,
+                                              need_output=False)
                 cs = [o[1] for o in outs]
                 del saved, outs
             inputs[i] = None
@@ -906,7 +914,8 @@ class LlamaModel:
             if ctx is None:
                 with timers.layer("recompute", layer.index):
                     _, ctx = layer.forward(inputs[i], batch.pos, self.rope_table, core_attn, True,
-                                           saved_attn=store.load(layer.index) if store is not None else None)
+                                           saved_attn=store.load(layer.index) if store is not None else None,
+                                           need_output=False)
             inputs[i] = None
             with timers.layer("bwd", layer.index):
                 dx = layer.backward(ctx, dx, batch.pos, self.rope_table, core_attn)

@@ -165,7 +165,9 @@ def default_time_model(kind: str = "b200"):
     if kind == "b200":
         tm.attn_len = [2048.0, 8192.0, 32768.0, 131072.0]
         tm.attn_ms = [0.0415, 0.535, 7.24, 112.0]
-        tm.linear_ms_per_token = 0.0
+        # everything of a Llama-3-8B layer that is not core attention, forward only, per token, from the phase
+        # timers of a 128K-token step on one GPU (GEMMs forward 1443 ms + norms + SwiGLU over 32 layers)
+        tm.linear_ms_per_token = 1480.0 / 32 / 131072
         tm.link_gbytes_per_s = 770.0
     elif kind == "h100":
         tm.attn_len = [4096.0, 8192.0, 16384.0, 32768.0, 65536.0]

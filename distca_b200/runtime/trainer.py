@@ -244,13 +244,27 @@ class Trainer:
         runs on the GPU (the C++ planner releases the GIL). ``train_step`` picks the plan up when it is
         given the same documents; otherwise it plans synchronously. The reference plans step N+1
         inside its data loader for the same reason (distca/planner/planner.py:411-507)."""
-        if self.nano != 1 or (self.cad is not None and not hasattr(self.cad, "make_plan")):
+        if isinstance(hb_next, SpanHostBatch) or (self.cad is not None and not hasattr(self.cad, "make_tables")):
             return
-        if self.cad is not None and self.cad.arena is None:
+        if self.cad is not None and any(ca.arena is None for ca in self.core_attns):
             return                   # the first plan sizes the arena: a collective, done in plan_step
         if self._plan_pool is None:
             from concurrent.futures import ThreadPoolExecutor
             self._plan_pool = ThreadPoolExecutor(max_workers=1, thread_name_prefix="cad-planner")
+        if self.nano == 2:
+            if self.cad is None:
+                return
+            # ping-pong: one plan per nano-batch, each for its own core-attention module
+            docs2 = [[list(d) for d in n.all_doc_lens] for n in split_nano(hb_next)]
+
+            def work2(cas=list(self.core_attns), docs2=docs2):
+                out = []
+                for ca, docs in zip(cas, docs2):
+                    plan = ca.make_plan(docs)
+                    out.append((plan, ca.make_tables(plan) if plan.fits else None))
+                return out
+            self._plan_ahead = (docs2, self._plan_pool.submit(work2))
+            return
         if self.cad is None:
             # local attention: the work lists of the next step are built on the worker thread
             mine = list(hb_next.doc_lens)
@@ -291,12 +305,21 @@ class Trainer:
     def plan_attention_nano(self, nano: list[HostBatch]) -> None:
         """One plan per nano-batch, each on its own core-attention module."""
         whole = max(sum(a) + sum(b) for a, b in zip(nano[0].all_doc_lens, nano[1].all_doc_lens))
-        for ca, hb in zip(self.core_attns, nano):
+        ahead = [None, None]
+        if self._plan_ahead is not None:
+            docs2, fut = self._plan_ahead
+            self._plan_ahead = None
+            if docs2 == [[list(d) for d in n.all_doc_lens] for n in nano]:
+                ahead = fut.result()
+        for k, (ca, hb) in enumerate(zip(self.core_attns, nano)):
             if self.cad is not None:
                 if hasattr(ca, "capacity_hint"):
                     # a nano-batch can be as large as the whole sequence (one long document)
                     ca.capacity_hint = max(ca.capacity_hint, whole)
-                ca.plan_step(hb.all_doc_lens, self.dp_rank)
+                if ahead[k] is not None:
+                    ca.plan_step(hb.all_doc_lens, self.dp_rank, plan=ahead[k][0], tables=ahead[k][1])
+                else:
+                    ca.plan_step(hb.all_doc_lens, self.dp_rank)
             else:
                 ca.set_batch(AttnPlan(AttnTasks.from_doc_lens(hb.doc_lens), self.device))
 

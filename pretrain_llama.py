@@ -95,7 +95,9 @@ def parse_args(argv=None):
     ap.add_argument("--attention-policy", default="cad", choices=["cad", "cp", "water_fill"],
                     help="cad: balanced core-attention disaggregation; cp: per-document context-parallel baseline")
     ap.add_argument("--tolerance", type=float, default=float(os.environ.get("MIN_TOLERANCE_FACTOR", 0.1)))
-    ap.add_argument("--pingpong", dest="pingpong", action="store_true", default=True)
+    ap.add_argument("--pingpong", dest="pingpong", action="store_true", default=False,
+                    help="two nano-batches per rank and step, interleaved layer by layer (the reference's ping-pong "
+                         "schedule); off by default, like bench.py: on one stream it measured the same speed")
     ap.add_argument("--no-pingpong", dest="pingpong", action="store_false")
     ap.add_argument("--save", default=None, help="checkpoint directory (Megatron layout)")
     ap.add_argument("--load", default=None)

@@ -180,3 +180,15 @@ def test_vectorised_backward_schedule_equals_the_loops():
         assert got == sorted(kv_ref)
         sizes = [int(r["qt_end"]) - int(r["qt_begin"]) for r in kv]
         assert sizes == sorted(sizes, reverse=True)          # heaviest key tiles first
+
+
+def test_layout_search_enumerates_every_factorisation_and_prefers_disaggregation_for_skewed_batches():
+    from distca_b200.planner.tools import search_layouts
+    res = search_layouts("llama3-8b", 8, 32768, "mixture", iterations=2)
+    got = {(r["tp"], r["pp"], r["dp"]) for r in res["layouts"]}
+    assert {(1, 1, 8), (2, 2, 2), (8, 1, 1), (4, 2, 1)} <= got and all(t * p * d == 8 for t, p, d in got)
+    for r in res["layouts"]:
+        if r["dp"] * r["pp"] > 1:
+            assert r["step_ms_cad"] <= r["step_ms_local_attention"] * 1.02
+        else:
+            assert r["step_ms_cad"] == r["step_ms_local_attention"]       # one server: nothing to disaggregate
