@@ -277,6 +277,12 @@ class LayerCtx:
     act: torch.Tensor
 
 
+def _on(streams, k: int):
+    """Context that queues what follows on ``streams[k]`` (no-op without streams)."""
+    import contextlib
+    return torch.cuda.stream(streams[k]) if streams is not None else contextlib.nullcontext()
+
+
 class LlamaLayer:
     def __init__(self, cfg: ModelConfig, store: ParamStore, index: int, tp=None):
         self.cfg, self.index = cfg, index
@@ -394,68 +400,92 @@ class LlamaLayer:
             return y, None
         return y, LayerCtx(x, rstd1, n1f, ca_ctx, attn_out, h, rstd2, n2f, pre, act)
 
-    def forward_nano(self, xs, poss, rope_table, cas, keep: bool, stores=None, saved=None, need_output: bool = True):
+    def forward_nano(self, xs, poss, rope_table, cas, keep: bool, stores=None, saved=None, need_output: bool = True,
+                     streams=None):
         """Forward of this layer for several nano-batches, ping-pong order: every nano-batch runs
         pre-CA (which dispatches its Q/K/V), then every attention server call is issued, and only then
         does each nano-batch collect its attention output and run post-CA, so one nano-batch's
         communication and attention overlap the other's linear layers. ``xs[k]`` is ``None`` when this
         rank owns no tokens of nano-batch ``k`` (it still serves attention for it).
+        ``streams``: one CUDA stream per nano-batch; every kernel of nano-batch ``k`` (its signal waits
+        included) is queued on ``streams[k]``, so while one nano-batch waits for its servers the GPU runs the
+        other's kernels (the reference's compute / communication stream pair with ``TickSync``,
+        distca/runtime/megatron/ping_pong/transformer_block.py:122-129, 234-344, ops/stream_sync_fn.py:80-136).
         Reference: distca/runtime/megatron/ping_pong/transformer_layer.py:260-417."""
         n = len(xs)
         pre = [None] * n
         for k in range(n):
-            if xs[k] is None:
-                cas[k].no_tokens_dispatch()
-            else:
-                pre[k] = self.pre_ca(xs[k], poss[k], rope_table, cas[k])
+            with _on(streams, k):
+                if xs[k] is None:
+                    cas[k].no_tokens_dispatch()
+                else:
+                    pre[k] = self.pre_ca(xs[k], poss[k], rope_table, cas[k])
         saving = stores is not None and not keep     # keep_attn: O and its statistics are stored per layer
         if saved is None:
-            with timers.phase("attn_fwd"):
-                for k in range(n):
+            for k in range(n):
+                with _on(streams, k), timers.phase("attn_fwd"):
                     cas[k].forward_begin(pre[k][0] if pre[k] is not None else None, self.index)
         outs = []
         for k in range(n):
-            if saved is None:
-                with timers.phase("attn_fwd"):
-                    attn_out, ca_ctx = cas[k].forward_end()
-            if xs[k] is None:
+            with _on(streams, k):
+                if saved is None:
+                    with timers.phase("attn_fwd"):
+                        attn_out, ca_ctx = cas[k].forward_end()
+                if xs[k] is None:
+                    if saved is not None:
+                        cas[k].restore_no_tokens(self.index)
+                    outs.append((None, None))
+                    continue
+                qkv, n1f, rstd1 = pre[k]
                 if saved is not None:
-                    cas[k].restore_no_tokens(self.index)
-                outs.append((None, None))
-                continue
-            qkv, n1f, rstd1 = pre[k]
-            if saved is not None:
-                attn_out, ca_ctx = cas[k].restore(qkv, saved[k], self.index)
-            elif saving:
-                stores[k].save(self.index, cas[k].pack_saved(attn_out, ca_ctx), clone=False)
-            y, h, rstd2, n2f, prea, act = self.post_ca(xs[k], attn_out, keep, need_output)
-            outs.append((y, LayerCtx(xs[k], rstd1, n1f, ca_ctx, attn_out, h, rstd2, n2f, prea, act) if keep else None))
+                    attn_out, ca_ctx = cas[k].restore(qkv, saved[k], self.index)
+                elif saving:
+                    stores[k].save(self.index, cas[k].pack_saved(attn_out, ca_ctx), clone=False)
+                y, h, rstd2, n2f, prea, act = self.post_ca(xs[k], attn_out, keep, need_output)
+                outs.append((y, LayerCtx(xs[k], rstd1, n1f, ca_ctx, attn_out, h, rstd2, n2f, prea, act) if keep else None))
         return outs
 
-    def backward_nano(self, cs, dys, poss, rope_table, cas):
+    def backward_nano(self, cs, dys, poss, rope_table, cas, streams=None):
         """Backward twin of :meth:`forward_nano`: post-CA backward + dO dispatch for every nano-batch,
-        then the attention-server backward calls, then collect and pre-CA backward."""
+        then the attention-server backward calls, then collect and pre-CA backward. With ``streams`` the
+        nano-batches run on their own streams; both accumulate into the same weight-gradient buffers, so the
+        second nano-batch's half of a layer starts after the first one's half has finished (an event), which is
+        the order the kernels would take on one stream anyway."""
         n = len(cs)
         dhs = [None] * n
+        done = None
         for k in range(n):
-            if cs[k] is None:
-                cas[k].backward_dispatch(None, None, self.index)
-                continue
-            dattn, dhs[k] = self.bwd_post_ca(cs[k], dys[k])
-            cas[k].backward_dispatch(cs[k].ca_ctx, dattn, self.index)
-            del dattn
-        with timers.phase("attn_bwd"):
-            for k in range(n):
+            with _on(streams, k):
+                if cs[k] is None:
+                    cas[k].backward_dispatch(None, None, self.index)
+                    continue
+                if streams is not None and done is not None:
+                    streams[k].wait_event(done)
+                dattn, dhs[k] = self.bwd_post_ca(cs[k], dys[k])
+                if streams is not None:
+                    done = torch.cuda.Event()
+                    done.record(streams[k])
+                cas[k].backward_dispatch(cs[k].ca_ctx, dattn, self.index)
+                del dattn
+        for k in range(n):
+            with _on(streams, k), timers.phase("attn_bwd"):
                 cas[k].backward_serve(self.index)
         dxs = []
+        done = None
         for k in range(n):
-            with timers.phase("attn_bwd"):
-                dqkv = cas[k].backward_end()
-            if cs[k] is None:
-                dxs.append(None)
-                continue
-            cs[k].ca_ctx = None
-            dxs.append(self.bwd_pre_ca(cs[k], dqkv, dhs[k], poss[k], rope_table))
+            with _on(streams, k):
+                with timers.phase("attn_bwd"):
+                    dqkv = cas[k].backward_end()
+                if cs[k] is None:
+                    dxs.append(None)
+                    continue
+                cs[k].ca_ctx = None
+                if streams is not None and done is not None:
+                    streams[k].wait_event(done)
+                dxs.append(self.bwd_pre_ca(cs[k], dqkv, dhs[k], poss[k], rope_table))
+                if streams is not None:
+                    done = torch.cuda.Event()
+                    done.record(streams[k])
         return dxs
 
     # ---- backward pieces ----
@@ -625,6 +655,8 @@ class LlamaModel:
         self._stores = None
         self._pinned = []
         self.grad_ready_hook = None        # called with a layer's parameter names once its gradients are final
+        self.nano_streams = True           # ping-pong: every nano-batch on its own CUDA stream
+        self._nano_stream_objs = None
         self.store_sync_group = None       # gloo-capable group over which the keep_attn placement is agreed
         self.attn_store_placement = None   # "device" | "host" to override the automatic choice
 
@@ -805,10 +837,22 @@ class LlamaModel:
     def forward_backward_nano(self, batches, cas):
         """One step over several nano-batches interleaved layer by layer (ping-pong). ``batches[k]`` is
         ``None`` when this rank has no tokens of nano-batch ``k``. Gradients of all nano-batches
-        accumulate into the same buffers; returns the summed loss."""
+        accumulate into the same buffers; returns the summed loss. With ``self.nano_streams`` every
+        nano-batch runs on its own CUDA stream (see :meth:`LlamaLayer.forward_nano`)."""
         assert self.first_stage and self.last_stage
         n = len(batches)
-        xs = [self.embed(b.ids) if b is not None else None for b in batches]
+        streams = None
+        if self.nano_streams and self.device.type == "cuda":
+            if self._nano_stream_objs is None or len(self._nano_stream_objs) != n:
+                self._nano_stream_objs = [torch.cuda.Stream(self.device) for _ in range(n)]
+            streams = self._nano_stream_objs
+            main = torch.cuda.current_stream(self.device)
+            for st_ in streams:
+                st_.wait_stream(main)          # zero_grad and the host-to-device copies come first
+        xs = []
+        for k, b in enumerate(batches):
+            with _on(streams, k):
+                xs.append(self.embed(b.ids) if b is not None else None)
         poss = [b.pos if b is not None else None for b in batches]
         nl = len(self.layers)
         stores = None
@@ -820,16 +864,23 @@ class LlamaModel:
             inputs.append(xs)
             use = stores if stores is not None and stores[0].has(layer.index) else None
             with timers.layer("fwd", layer.index):
-                outs = layer.forward_nano(xs, poss, self.rope_table, cas, keep, stores=use)
+                outs = layer.forward_nano(xs, poss, self.rope_table, cas, keep, stores=use, streams=streams)
             xs = [o[0] for o in outs]
             ctxs.append([o[1] for o in outs] if keep else None)
-        loss = torch.zeros((), dtype=torch.float32, device=self.device)
+        losses = []
         dxs = [None] * n
-        with timers.phase("lm_head"):
-            for k in range(n):
-                if xs[k] is not None:
-                    l, dxs[k] = self.head_loss_and_grad(xs[k], batches[k].labels, batches[k].num_valid_global)
-                    loss = loss + l
+        done = None
+        for k in range(n):
+            if xs[k] is None:
+                continue
+            with _on(streams, k), timers.phase("lm_head"):
+                if streams is not None and done is not None:
+                    streams[k].wait_event(done)          # the LM head's gradient accumulators are shared
+                l, dxs[k] = self.head_loss_and_grad(xs[k], batches[k].labels, batches[k].num_valid_global)
+                losses.append(l)
+                if streams is not None:
+                    done = torch.cuda.Event()
+                    done.record(streams[k])
         del xs
         for i in reversed(range(nl)):
             layer = self.layers[i]
@@ -838,26 +889,43 @@ class LlamaModel:
             if cs is None:
                 saved = None
                 if stores is not None and stores[0].has(layer.index):
-                    saved = [st.load(layer.index) if inputs[i][k] is not None else None for k, st in enumerate(stores)]
-                    if i > 0:
-                        for k, st in enumerate(stores):
-                            if inputs[i][k] is not None:
+                    saved = []
+                    for k, st in enumerate(stores):
+                        with _on(streams, k):
+                            saved.append(st.load(layer.index) if inputs[i][k] is not None else None)
+                            if i > 0 and inputs[i][k] is not None:
                                 st.prefetch(self.layers[i - 1].index)
                 with timers.layer("recompute", layer.index):
                     outs = layer.forward_nano(inputs[i], poss, self.rope_table, cas, True, saved=saved,
-                                              need_output=False)
+                                              need_output=False, streams=streams)
                 cs = [o[1] for o in outs]
                 del saved, outs
             inputs[i] = None
             with timers.layer("bwd", layer.index):
-                dxs = layer.backward_nano(cs, dxs, poss, self.rope_table, cas)
+                dxs = layer.backward_nano(cs, dxs, poss, self.rope_table, cas, streams=streams)
             del cs
             if self.grad_ready_hook is not None:
+                if streams is not None:
+                    for st_ in streams:
+                        torch.cuda.current_stream(self.device).wait_stream(st_)
                 self.grad_ready_hook(list(layer.names.values()))
-        with timers.phase("embed_bwd"):
-            for k in range(n):
-                if dxs[k] is not None:
-                    self.embed_bwd(batches[k].ids, dxs[k])
+        done = None
+        for k in range(n):
+            if dxs[k] is None:
+                continue
+            with _on(streams, k), timers.phase("embed_bwd"):
+                if streams is not None and done is not None:
+                    streams[k].wait_event(done)
+                self.embed_bwd(batches[k].ids, dxs[k])
+                if streams is not None:
+                    done = torch.cuda.Event()
+                    done.record(streams[k])
+        if streams is not None:
+            for st_ in streams:
+                torch.cuda.current_stream(self.device).wait_stream(st_)
+        loss = torch.zeros((), dtype=torch.float32, device=self.device)
+        for l in losses:
+            loss = loss + l
         return loss, None
 
     def _attn_stores(self, tokens_per_nano: list):

@@ -93,7 +93,7 @@ def _memory_bound_case(name: str, a, dev):
             ew.ce_grad(logits, lab, st, 1.0, dlogits=dl)
         return fn, Tc * V * (4.0 + 4.0 + 2.0), [Tc, V]
     if name == "adam":
-        n = 1 << 30
+        n = a.flat_elems
         p = torch.randn(n, device=dev).to(bf); lo = torch.zeros(n, device=dev, dtype=torch.int16)
         g = torch.randn(n, device=dev).to(bf); m = torch.zeros(n, device=dev); v = torch.zeros(n, device=dev)
         return (lambda: ew.adam_step_(p, lo, g, m, v, lr=1e-5, beta1=0.9, beta2=0.95, eps=1e-8, weight_decay=0.01,
@@ -118,8 +118,8 @@ def _memory_bound_case(name: str, a, dev):
         o = torch.randn(T, Hq, D, device=dev).to(bf); do = torch.randn(T, Hq, D, device=dev).to(bf)
         return (lambda: A.attn_delta_rows(o, do)), 2.0 * T * Hq * D * 2, [T, Hq, D]
     if name == "zero":
-        z = torch.empty(1 << 30, device=dev, dtype=bf)
-        return (lambda: z.zero_()), 2.0 * (1 << 30), [1 << 30]
+        z = torch.empty(a.flat_elems, device=dev, dtype=bf)
+        return (lambda: z.zero_()), 2.0 * a.flat_elems, [a.flat_elems]
     raise ValueError(name)
 
 
@@ -131,11 +131,54 @@ def _swiglu_bwd_out(pre, dact, out):
     _lib.check_rc(rc, "swiglu_bwd")
 
 
+def _attn_sweep(a, dev, flush, peaks, src) -> None:
+    """Forward and backward time over (document length x documents) workloads, one JSON line each, then the
+    least-squares fit ``ms = a * tile_pairs + b * query_tiles`` of forward + backward: the constants of the
+    planner's cost model (``distca_b200.planner.default_cost_model``) and the attention table of its time
+    model come from this table. The reference's counterpart is its FlashAttention latency profile
+    (distca/profiling/modal-scripts/attn-prof.py:20-99 -> distca/profiling/data/compute-attn-H100.csv)."""
+    import numpy as np
+    from ..ops import _lib, attention as A
+    Hq, Hkv, D = a.heads_q, a.heads_kv, 128
+    cases = [(2048, 16), (4096, 8), (8192, 1), (8192, 4), (16384, 1), (32768, 1), (65536, 1), (131072, 1)]
+    X, y = [], []
+    for L, docs in cases:
+        T = L * docs
+        q = torch.randn(T, Hq, D, device=dev).bfloat16()
+        k = torch.randn(T, Hkv, D, device=dev).bfloat16()
+        v = torch.randn(T, Hkv, D, device=dev).bfloat16()
+        tasks = A.AttnTasks.from_doc_lens([L] * docs)
+        plan = A.AttnPlan(tasks, dev)
+        o, lse = torch.empty_like(q), torch.empty(T, Hq, device=dev)
+        do = torch.randn_like(q)
+        dq, dk, dv = torch.empty_like(q), torch.empty_like(k), torch.empty_like(v)
+        iters = 1 if L >= 65536 else a.iters
+        f = _time(lambda: A.flash_fwd(q, k, v, plan, out=o, lse=lse), iters, 1 if L >= 65536 else a.warmup, flush)
+        b = _time(lambda: A.flash_bwd(q, k, v, o, lse, do, plan, dq=dq, dk=dk, dv=dv), iters, 1, flush)
+        n = L // 128
+        pairs, qtiles = docs * n * (n + 1) // 2, docs * n
+        fl = tasks.flops_fwd(Hq, D)
+        print(json.dumps({"kernel": "attn_sweep", "seqlen": L, "docs": docs, "fwd_ms": f, "bwd_ms": b,
+                          "fwd_tflops": fl / f / 1e9, "bwd_tflops_2p5x": 2.5 * fl / b / 1e9,
+                          "tile_pairs": pairs, "query_tiles": qtiles, "peak_source": src}))
+        X.append([pairs, qtiles]); y.append(f + b)
+        del q, k, v, o, do, dq, dk, dv
+        torch.cuda.empty_cache()
+    _lib.check_status()
+    X, y = np.asarray(X, dtype=np.float64), np.asarray(y)
+    w = 1.0 / y                                   # relative error: every workload counts alike
+    coef, *_ = np.linalg.lstsq(X * w[:, None], y * w, rcond=None)
+    pred = X @ coef
+    print(json.dumps({"kernel": "attn_sweep_fit", "heads_q": Hq, "ms_per_tile_pair": float(coef[0]),
+                      "ms_per_q_tile": float(coef[1]),
+                      "max_rel_err": float(np.max(np.abs(pred - y) / y))}))
+
+
 def main() -> None:
     ap = argparse.ArgumentParser()
     ap.add_argument("--kernel", required=True,
-                    choices=["gemm", "gemm_dgrad", "gemm_wgrad", "gemm_swiglu", "attn_fwd", "attn_bwd", *MEMORY_BOUND,
-                             "memory_bound"],
+                    choices=["gemm", "gemm_dgrad", "gemm_wgrad", "gemm_swiglu", "attn_fwd", "attn_bwd", "attn_sweep",
+                             *MEMORY_BOUND, "memory_bound"],
                     help="memory_bound: every kernel of the elementwise / loss / optimizer / row-copy family, one line each")
     ap.add_argument("--m", type=int, default=8192)
     ap.add_argument("--n", type=int, default=6144)
@@ -150,6 +193,7 @@ def main() -> None:
     ap.add_argument("--hidden", type=int, default=4096)
     ap.add_argument("--ffn", type=int, default=14336)
     ap.add_argument("--vocab", type=int, default=128256)
+    ap.add_argument("--flat-elems", type=int, default=1 << 30, help="elements of the optimizer / memset cases")
     ap.add_argument("--hbm-gbs", type=float, default=0.0, help="copy bandwidth to report fractions against")
     ap.add_argument("--bf16-tflops", type=float, default=0.0, help="bf16 GEMM throughput to report fractions against")
     ap.add_argument("--peaks-file", default=None, help="JSON with hbm_gbs and bf16_tflops")
@@ -160,6 +204,9 @@ def main() -> None:
     flush = torch.empty(256 << 20, dtype=torch.uint8, device=dev)  # > 126 MB L2
     peaks, src = _peaks(a)
     out = {"kernel": a.kernel}
+    if a.kernel == "attn_sweep":
+        _attn_sweep(a, dev, flush, peaks, src)
+        return
     if a.kernel.startswith("gemm"):
         M, N, K = a.m, a.n, a.k
         x = torch.randn(M, K, device=dev).bfloat16()

@@ -19,6 +19,7 @@ class PhaseTimers:
     distca/runtime/megatron/ping_pong/transformer_block.py:242-341)."""
 
     def __init__(self, enabled: bool = False, nvtx: bool = False):
+        self.prefix = ""            # prepended to phase names (the recompute pass reports as "re_<phase>")
         self.enabled = enabled and torch.cuda.is_available()
         self.nvtx = nvtx and torch.cuda.is_available()
         self._pairs: dict[str, list] = defaultdict(list)
@@ -28,6 +29,7 @@ class PhaseTimers:
         if not self.enabled and not self.nvtx:
             yield
             return
+        name = self.prefix + name
         if self.nvtx:
             torch.cuda.nvtx.range_push(name)
         if self.enabled:
@@ -67,15 +69,19 @@ def enable_nvtx(flag: bool = True) -> None:
 
 @contextmanager
 def layer(kind: str, index: int):
-    """NVTX range around one layer's forward / recompute / backward (no timing)."""
-    if not GLOBAL.nvtx:
-        yield
-        return
-    torch.cuda.nvtx.range_push(f"{kind}.layer{index}")
+    """NVTX range around one layer's forward / recompute / backward; phases inside a recompute pass are
+    reported under ``re_<phase>`` so that forward and recompute time can be told apart."""
+    old = GLOBAL.prefix
+    if kind == "recompute":
+        GLOBAL.prefix = "re_"
+    if GLOBAL.nvtx:
+        torch.cuda.nvtx.range_push(f"{kind}.layer{index}")
     try:
         yield
     finally:
-        torch.cuda.nvtx.range_pop()
+        GLOBAL.prefix = old
+        if GLOBAL.nvtx:
+            torch.cuda.nvtx.range_pop()
 
 
 def phase(name: str):

@@ -226,8 +226,8 @@ def main(argv=None) -> int:
             rec["attn_imbalance"] = cad_rt.plan_stats.get("imbalance_after")
             rec["attn_time_imbalance_measured"] = cad_rt.plan_stats.get("attention_time_imbalance")
             ph = timers.GLOBAL.summary(reset=not a.phase_timers) if timers.GLOBAL.enabled else {}
-            rec["exposed_dispatch_ms"] = (sum(v for k, v in ph.items() if k.startswith("cad_wait") or
-                                              k in ("cad_dispatch", "cad_return")) if ph else None)
+            rec["exposed_dispatch_ms"] = (sum(v for k, v in ph.items() if k.removeprefix("re_").startswith("cad_wait") or
+                                              k.removeprefix("re_") in ("cad_dispatch", "cad_return")) if ph else None)
             if cad_rt.last_plan is not None:
                 art.plan({"step": it, **inspect_plan(cad_rt.last_plan, cad_rt.W)})
         if a.phase_timers:

@@ -88,3 +88,11 @@ def test_cad_tp2_dp2_fused_transports():
     """Tensor parallel (GEMM-fused all-gather / reduce-scatter) x data parallel (peer reduce-scatter + Adam)."""
     res = _run(4, 29549, ["--tokens", "8192", "--tp", "2"])
     assert res["ok"], res
+
+
+@pytest.mark.skipif(_ngpu() < 2, reason="needs 2 GPUs")
+def test_cad_dp2_pingpong_two_streams():
+    """Two nano-batches per rank, each on its own CUDA stream with its own plan, arena and signals; gradients of
+    both accumulate into the same buffers (ordered by events)."""
+    res = _run(2, 29550, ["--tokens", "8192", "--nano", "2", "--recompute", "keep_attn"])
+    assert res["ok"], res
