@@ -438,6 +438,25 @@ def main() -> None:
         if a.phase_timers:
             out["phases_ms_per_step"] = {k: round(v / a.steps, 2) for k, v in sorted(phases.items())}
         if trainer.cad is not None:
+            # achieved / roofline of the fused compute + communication paths (rank 0's traffic of the last plan)
+            from distca_b200.utils.observability import fused_path_rooflines
+            peaks = {"bf16_tflops": 1590.0, "hbm_gbs": 6650.0, "link_gbs": 770.0, "source": "fallback"}
+            pk = os.path.join(os.path.dirname(os.path.abspath(__file__)), "MEASURED_PEAKS.json")
+            if os.path.exists(pk):
+                with open(pk) as f:
+                    mp = json.load(f)
+                peaks.update(bf16_tflops=mp["bf16_tflops_sustained"], hbm_gbs=mp["hbm_gbs"], source="measured (sustained GEMM)")
+            sb = trainer.cad.plan_stats.get("send_bytes", [0] * world)
+            remote = float(sum(sb) - sb[trainer.cad.me])
+            q_share = cfg.q_dim / (cfg.q_dim + 2.0 * cfg.kv_dim)        # the return trip carries O (forward) / dQ + copies (backward)
+            nparam = trainer.model.store.numel
+            gb = trainer.model.store.grad.element_size()
+            out["roofline"] = {"peaks": peaks, "paths": fused_path_rooflines(
+                phases, a.steps, tokens_per_rank=a.seq_len, hidden=cfg.hidden, qkv_dim=cfg.qkv_dim, layers=cfg.num_layers,
+                passes_qkv=2, attn_flops_fwd_per_rank=attn_flop / 3.0 / a.steps / world, remote_dispatch_bytes=remote,
+                remote_return_bytes=remote * q_share, grad_bytes_in=nparam * gb * (world - 1) / world,
+                param_bytes_out=nparam * 2 * (world - 1) / world,
+                optimizer_hbm_bytes=nparam / world * (gb * world + 2 + 2 + 16 + 2 * world), peaks=peaks)}
             out["cad"] = {"planned_imbalance_after": trainer.cad.plan_stats.get("imbalance_after"),
                           "planned_imbalance_before": trainer.cad.plan_stats.get("imbalance_before"),
                           "planned_cost_imbalance_after": trainer.cad.plan_stats.get("cost_imbalance_after"),

@@ -6,7 +6,10 @@
 Nodes are reached with ``ssh`` (the first one is the rendezvous host); ``--nodes localhost`` or no
 ``--nodes`` runs in place without ssh. ``{hostname}`` in the command is replaced per node and each node's
 output is streamed and, with ``--output-dir``, saved as ``<hostname>.log``. ``--dry-run`` prints the
-commands only. The reference does the same job with one Ray task per 8-GPU node
+commands only. ``--nsys PREFIX`` wraps every node's ``torchrun`` in ``nsys profile -o PREFIX.<hostname>
+--trace=cuda,nvtx`` (the reference's ``ENABLE_NSYS`` switch, pretrain_llama.sh:243-246; run the script with
+``--nvtx`` to get per-tick / per-layer / per-phase ranges; ``nsys`` itself must be installed on the nodes).
+The reference does the same job with one Ray task per 8-GPU node
 (distca/ray_launch.py:11-137); Ray is not a dependency here.
 """
 from __future__ import annotations
@@ -20,7 +23,8 @@ import threading
 
 
 def build_commands(nodes: list[str], gpus_per_node: int, script_args: list[str], port: int = 29500,
-                   workdir: str | None = None, python: str = sys.executable) -> list[tuple[str, str]]:
+                   workdir: str | None = None, python: str = sys.executable, nsys: str | None = None
+                   ) -> list[tuple[str, str]]:
     """(node, shell command) per node."""
     master = "127.0.0.1" if nodes == ["localhost"] else nodes[0]
     out = []
@@ -28,6 +32,8 @@ def build_commands(nodes: list[str], gpus_per_node: int, script_args: list[str],
         args = [a.replace("{hostname}", node) for a in script_args]
         cmd = [python, "-m", "torch.distributed.run", f"--nnodes={len(nodes)}", f"--node-rank={rank}",
                f"--nproc-per-node={gpus_per_node}", "--master-addr", master, "--master-port", str(port), *args]
+        if nsys:
+            cmd = ["nsys", "profile", "-o", f"{nsys}.{node}", "--trace=cuda,nvtx", "--force-overwrite=true", *cmd]
         line = " ".join(shlex.quote(c) for c in cmd)
         if workdir:
             line = f"cd {shlex.quote(workdir)} && {line}"
@@ -57,13 +63,14 @@ def main(argv=None) -> int:
     ap.add_argument("--output-dir", default=None)
     ap.add_argument("--no-duplicate-log", action="store_true", help="print only the first node's output")
     ap.add_argument("--dry-run", action="store_true")
+    ap.add_argument("--nsys", default=None, metavar="PREFIX", help="profile every node's run with nsys into PREFIX.<hostname>")
     ap.add_argument("script", nargs=argparse.REMAINDER, help="-- script.py args...")
     a = ap.parse_args(argv)
     script = a.script[1:] if a.script and a.script[0] == "--" else a.script
     if not script:
         ap.error("nothing to launch")
     nodes = [n for n in a.nodes.split(",") if n]
-    cmds = build_commands(nodes, a.gpus_per_node, script, a.port, a.workdir)
+    cmds = build_commands(nodes, a.gpus_per_node, script, a.port, a.workdir, nsys=a.nsys)
     if a.dry_run:
         for node, c in cmds:
             print(f"[{node}] {c}")

@@ -319,14 +319,14 @@ class LlamaLayer:
             with timers.phase("norm"):
                 buf = fused.stage_buffer(x.shape[0], x.shape[1])
                 _, rstd1 = ew.rmsnorm_fwd(x, self.w["ln1"], self.cfg.norm_eps, out=buf)
-            with timers.phase("gemm_fwd"):
+            with timers.phase("gemm_qkv"):
                 qkv = fused.ag_linear(buf, self.w["wqkv"], rope=rope)
             n1f = buf.clone()   # local shard only; gathered again for the weight gradient
         else:
             with timers.phase("norm"):
                 n1, rstd1 = ew.rmsnorm_fwd(x, self.w["ln1"], self.cfg.norm_eps)
             n1f = self.tp.all_gather_rows(n1)
-            with timers.phase("gemm_fwd"):
+            with timers.phase("gemm_qkv"):
                 if rope is not None:
                     qkv = gemm.linear_qkv_rope(n1f, self.w["wqkv"], **rope)
                 else:

@@ -345,6 +345,8 @@ class Trainer:
             # baseline: every rank holds a head and a tail chunk of every document of the global batch
             from ..parallel.percp import percp_layout
             W = self.percp.W
+            if self.par.tp > 1:
+                self.model.tp.ensure_fused(int(hb.tokens.numel()) // W // self.par.tp)
             with timers.phase("plan"):
                 ids, labels, pos = hb.materialise(percp_layout(hb.doc_lens, W, self.percp.me),
                                                   int(hb.tokens.numel()) // W, pinned=self.device.type == "cuda")

@@ -40,10 +40,17 @@ from ..runtime.trainer import init_distributed
 
 
 def _documents(rng, world: int, T: int) -> list[list[int]]:
-    docs = []
-    while len(docs) < world:
-        lens = sample_loguniform(rng, 64, 128, T)
-        docs += pack_documents(lens, T, max_packs=world - len(docs))
+    """One pack of ``T`` tokens per rank, document lengths log-uniform in [128, T]; batches whose causal work is
+    already balanced (max / mean of the ranks' sum of L^2 below 1.3) are drawn again, so that every payload size
+    of the sweep has something to dispatch. Both arms call this with the same generator state."""
+    for _ in range(64):
+        docs = []
+        while len(docs) < world:
+            lens = sample_loguniform(rng, 64, 128, T)
+            docs += pack_documents(lens, T, max_packs=world - len(docs))
+        work = [sum(float(L) * L for L in d) for d in docs]
+        if max(work) >= 1.3 * (sum(work) / world):
+            break
     return docs
 
 

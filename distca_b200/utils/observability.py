@@ -187,3 +187,34 @@ class MetricsSink:
             self.run.finish()
         if self.file is not None:
             self.file.close()
+
+
+def fused_path_rooflines(phases_ms: dict, steps: int, *, tokens_per_rank: int, hidden: int, qkv_dim: int, layers: int,
+                         passes_qkv: int, attn_flops_fwd_per_rank: float, remote_dispatch_bytes: float,
+                         remote_return_bytes: float, grad_bytes_in: float, param_bytes_out: float,
+                         optimizer_hbm_bytes: float, peaks: dict) -> dict:
+    """Achieved / roofline of every fused compute + communication path of one step, from the CUDA-event phase
+    timers. The roofline time of a path is the slower of its FLOPs at the GEMM peak, its bytes over NVLink at the
+    link bandwidth and its bytes through HBM at the copy bandwidth (``peaks``: ``bf16_tflops``, ``hbm_gbs``,
+    ``link_gbs``). Times are per step and per rank; a fraction near 1 means the path runs at its roofline."""
+    def ph(*names):
+        return sum(v for k, v in phases_ms.items() if k.removeprefix("re_") in names) / max(1, steps)
+
+    def row(ms, flops=0.0, link_bytes=0.0, hbm_bytes=0.0):
+        t_f = flops / (peaks["bf16_tflops"] * 1e12) * 1e3
+        t_l = link_bytes / (peaks["link_gbs"] * 1e9) * 1e3
+        t_h = hbm_bytes / (peaks["hbm_gbs"] * 1e9) * 1e3
+        roof = max(t_f, t_l, t_h)
+        bound = {t_f: "tensor", t_l: "nvlink", t_h: "hbm"}[roof]
+        return {"ms": round(ms, 2), "roofline_ms": round(roof, 2), "bound": bound,
+                "fraction_of_roofline": round(roof / ms, 3) if ms > 0 else None}
+    out = {}
+    qkv_flops = 2.0 * tokens_per_rank * hidden * qkv_dim * layers * passes_qkv
+    out["qkv_gemm_rope_dispatch"] = row(ph("gemm_qkv"), qkv_flops, remote_dispatch_bytes * layers * passes_qkv)
+    out["attention_forward_with_output_return"] = row(ph("cad_attn_fwd"), attn_flops_fwd_per_rank,
+                                                      remote_return_bytes * layers)
+    out["attention_backward_with_gradient_return"] = row(ph("cad_attn_bwd"), 2.5 * attn_flops_fwd_per_rank,
+                                                         (remote_dispatch_bytes + remote_return_bytes) * layers)
+    out["gradient_reduce_scatter_adam_all_gather"] = row(ph("optimizer"), 0.0, grad_bytes_in + param_bytes_out,
+                                                         optimizer_hbm_bytes)
+    return out

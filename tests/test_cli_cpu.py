@@ -100,3 +100,25 @@ def test_checkpoint_restores_rng_state(tmp_path):
     torch.manual_seed(99)
     assert load_checkpoint(str(tmp_path), m, opt, cfg) == 5
     assert torch.equal(torch.rand(4), want)
+
+
+def test_bench_named_configs_are_the_contract_layouts():
+    """bench.py --config: the three fixed 8-GPU layouts (TP=8 at 64K with 8 sequences per step; TP=2 x PP=2 x DP=2
+    at 128K; 34B shape at TP=4 x PP=2 and 256K with full recompute)."""
+    import importlib.util
+    spec = importlib.util.spec_from_file_location("bench_mod", os.path.join(ROOT, "bench.py"))
+    bench = importlib.util.module_from_spec(spec)
+    spec.loader.exec_module(bench)
+    from distca_b200.models.config import get_model_config
+    c = bench.NAMED_CONFIGS
+    assert set(c) == {"tp8_64k", "4d_128k", "34b_256k"}
+    for v in c.values():
+        assert v["tp"] * v["pp"] * v["dp"] == 8
+        cfg = get_model_config(v["model"])
+        assert cfg.heads_kv % v["tp"] == 0 and cfg.num_layers % v["pp"] == 0
+        assert v["pp"] == 1 or v["microbatches"] >= v["pp"]
+    assert (c["tp8_64k"]["seq_len"], c["tp8_64k"]["seqs_per_rank"]) == (65536, 8)
+    assert (c["4d_128k"]["tp"], c["4d_128k"]["pp"], c["4d_128k"]["dp"], c["4d_128k"]["seq_len"]) == (2, 2, 2, 131072)
+    m = get_model_config("codellama-34b")
+    assert (m.num_layers, m.hidden, m.heads_q, m.heads_kv, m.ffn, m.vocab) == (48, 8192, 64, 8, 22016, 32000)
+    assert c["34b_256k"]["recompute"] == "full" and c["34b_256k"]["seq_len"] == 262144
