@@ -313,15 +313,29 @@ class LlamaLayer:
             ep = core_attn.qkv_epilogue()
             if ep is not None:
                 rope = dict(ep, pos=pos, table=rope_table, heads_q=self.hq, heads_kv=self.hkv)
-        if fused is not None and x.shape[0] % 128 == 0:
-            # all-gather fused into the QKV GEMM: the normalised shard is written into the peer arena
-            # and every rank's GEMM reads the other shards over NVLink tile by tile
+        if fused is not None and x.shape[0] % 128 == 0 and fused.tile_loads:
+            # all-gather fused into the QKV GEMM's operand load: the normalised shard is written into the peer
+            # arena and every CTA reads the tile it needs from its owner over NVLink (each remote tile crosses
+            # the link once per N tile that uses it: only worth it for narrow outputs)
             with timers.phase("norm"):
                 buf = fused.stage_buffer(x.shape[0], x.shape[1])
                 _, rstd1 = ew.rmsnorm_fwd(x, self.w["ln1"], self.cfg.norm_eps, out=buf)
             with timers.phase("gemm_qkv"):
                 qkv = fused.ag_linear(buf, self.w["wqkv"], rope=rope)
             n1f = buf.clone()   # local shard only; gathered again for the weight gradient
+        elif fused is not None and x.shape[0] % 128 == 0:
+            # every rank stores its normalised shard into every peer's gather buffer (each shard crosses NVLink
+            # once), then the GEMM (with RoPE + dispatch in its epilogue) reads the gathered rows locally
+            with timers.phase("norm"):
+                n1f, rstd1 = ew.rmsnorm_fwd(x, self.w["ln1"], self.cfg.norm_eps)
+            with timers.phase("gemm_qkv"):
+                g = fused.all_gather_rows(n1f)
+                if rope is not None:
+                    qkv = gemm.linear_qkv_rope(g, self.w["wqkv"], **rope)
+                else:
+                    qkv = gemm.linear_fwd(g, self.w["wqkv"])
+                fused.release_gather()
+                del g
         else:
             with timers.phase("norm"):
                 n1, rstd1 = ew.rmsnorm_fwd(x, self.w["ln1"], self.cfg.norm_eps)
@@ -354,7 +368,7 @@ class LlamaLayer:
             else:
                 h = self.tp.reduce_scatter_rows(gemm.linear_fwd(attn_out, self.w["wo"]))
                 ew.add_(h, x)
-        if fused is not None:
+        if fused is not None and fused.tile_loads:
             # FC1: the normalised shard goes into the peer arena, the GEMM reads every rank's shard tile by tile
             # (all-gather fused into the operand load) and applies SwiGLU in its epilogue
             with timers.phase("norm"):
@@ -363,6 +377,15 @@ class LlamaLayer:
             with timers.phase("gemm_fwd"):
                 act, pre = fused.ag_linear_swiglu(buf, self.w["w13"], keep_preact=keep)
             n2f = buf.clone() if keep else None    # local shard only; gathered again for the weight gradient
+        elif fused is not None:
+            # FC1: shards gathered once by peer stores, SwiGLU in the epilogue of the local GEMM
+            with timers.phase("norm"):
+                n2f, rstd2 = ew.rmsnorm_fwd(h, self.w["ln2"], self.cfg.norm_eps)
+            with timers.phase("gemm_fwd"):
+                g = fused.all_gather_rows(n2f)
+                act, pre = gemm.linear_swiglu_fwd(g, self.w["w13"], keep_preact=keep)
+                fused.release_gather()
+                del g
         else:
             with timers.phase("norm"):
                 n2, rstd2 = ew.rmsnorm_fwd(h, self.w["ln2"], self.cfg.norm_eps)
@@ -520,18 +543,18 @@ class LlamaLayer:
         return dattn, dh
 
     def _bwd_post_ca_fused(self, c: LayerCtx, dy, fused):
-        """Tensor + sequence parallel backward of the post-attention half without NCCL: the data-gradient GEMMs
-        read the peers' shards in their operand loads (all-gather -> GEMM) or scatter their rows to the owners
-        in their epilogues (GEMM -> reduce-scatter); the weight-gradient GEMMs need the token dimension as their
-        reduction dimension, so their sharded operand is gathered by peer stores first (``all_gather_rows``)."""
+        """Tensor + sequence parallel backward of the post-attention half without NCCL: sharded operands are
+        gathered by peer stores (``all_gather_rows``: every shard crosses NVLink once and serves both the
+        data-gradient and the weight-gradient GEMM), and the GEMMs whose output is reduce-scattered store their
+        rows to the owners from their epilogues (GEMM -> reduce-scatter)."""
         rows, H = dy.shape
         with timers.phase("gemm_bwd"):
-            buf = fused.stage_buffer(rows, H)
-            buf.copy_(dy)
-            dact = fused.ag_linear(buf, self.w["w2"], transposed_weight=True)            # all_gather(dy) @ W2
+            # one gather of dy (peer stores) serves the data-gradient and the weight-gradient GEMM
             dyf = fused.all_gather_rows(dy)
+            dact = gemm.linear_dgrad(dyf, self.w["w2"])                                  # all_gather(dy) @ W2
             gemm.linear_wgrad(dyf, c.act, out=self.g["w2"], accumulate=True)
             fused.release_gather()
+            del dyf
         c.act = None
         with timers.phase("swiglu_bwd"):
             dpre = ew.swiglu_bwd(c.pre, dact, inplace=True)
@@ -549,12 +572,11 @@ class LlamaLayer:
             dh = ew.rmsnorm_bwd(c.h, self.w["ln2"], c.rstd2, dn2, self.g["ln2"], dres=dy)
         del dn2
         with timers.phase("gemm_bwd"):
-            buf = fused.stage_buffer(rows, H)
-            buf.copy_(dh)
-            dattn = fused.ag_linear(buf, self.w["wo"], transposed_weight=True)           # all_gather(dh) @ Wo
             dhf = fused.all_gather_rows(dh)
+            dattn = gemm.linear_dgrad(dhf, self.w["wo"])                                 # all_gather(dh) @ Wo
             gemm.linear_wgrad(dhf, c.attn_out, out=self.g["wo"], accumulate=True)
             fused.release_gather()
+            del dhf
         c.attn_out = c.h = None
         return dattn, dh
 

@@ -68,7 +68,8 @@ class PipelineTrainer:
             from .tensor_parallel import TensorParallel
             # default on GPUs: all-gather / reduce-scatter fused into the GEMMs over peer memory
             tp = TensorParallel(self.groups.tp_group, par.tp, self.tp_rank, self.device,
-                                use_p2p=train_cfg.extra.get("tp_transport", "p2p") == "p2p",
+                                use_p2p=train_cfg.extra.get("tp_transport", "p2p") in ("p2p", "p2p-tile"),
+                                tile_loads=train_cfg.extra.get("tp_transport", "p2p") == "p2p-tile",
                                 max_cols=model_cfg.hidden)
         per = model_cfg.num_layers // par.pp
         self.first, self.last = self.pp_rank == 0, self.pp_rank == par.pp - 1

@@ -19,7 +19,7 @@ import torch.distributed as dist
 
 class TensorParallel:
     def __init__(self, group, size: int, rank: int, device, use_p2p: bool = False, max_rows_local: int = 0,
-                 max_cols: int = 0):
+                 max_cols: int = 0, tile_loads: bool = False):
         self.group, self.size, self.rank = group, size, rank
         self.device = torch.device(device)
         self.on_gpu = self.device.type == "cuda"
@@ -27,6 +27,7 @@ class TensorParallel:
         self.nccl_row_collectives = 0   # all_gather_rows / reduce_scatter_rows calls that went to NCCL (diagnostic)
         self.use_p2p = use_p2p and self.on_gpu
         self._max_cols = max_cols
+        self._tile_loads = tile_loads
         if self.use_p2p and max_rows_local > 0:
             self.ensure_fused(max_rows_local)
 
@@ -41,7 +42,8 @@ class TensorParallel:
         if self.fused is not None:
             self.fused.close()
         from .tp_p2p import PeerCollectives
-        self.fused = PeerCollectives(self.group, self.size, self.rank, self.device, rows_local, self._max_cols)
+        self.fused = PeerCollectives(self.group, self.size, self.rank, self.device, rows_local, self._max_cols,
+                                     tile_loads=self._tile_loads)
 
     def all_gather_rows(self, x: torch.Tensor) -> torch.Tensor:
         self.nccl_row_collectives += 1

@@ -28,8 +28,13 @@ SIG_STAGED, SIG_READ, SIG_PARTIAL, SIG_SUMMED, SIG_GIN, SIG_GDONE = 0, 1, 2, 3, 
 
 
 class PeerCollectives:
-    def __init__(self, group, size: int, rank: int, device, max_rows_local: int, max_cols: int):
-        """``max_rows_local``: largest T/tp; ``max_cols``: largest K of ``ag_linear`` / N of ``linear_rs``."""
+    def __init__(self, group, size: int, rank: int, device, max_rows_local: int, max_cols: int,
+                 tile_loads: bool = False):
+        """``max_rows_local``: largest T/tp; ``max_cols``: largest K of ``ag_linear`` / N of ``linear_rs``.
+        ``tile_loads``: the model's all-gather -> GEMM sites use :meth:`ag_linear` / :meth:`ag_linear_swiglu`
+        (every CTA loads the remote tiles it needs: a remote tile crosses NVLink once per N tile that uses it)
+        instead of :meth:`all_gather_rows` + a local GEMM (every shard crosses once)."""
+        self.tile_loads = tile_loads
         self.size, self.rank = size, rank
         self.device = torch.device(device)
         self.max_rows, self.max_cols = max_rows_local, max_cols

@@ -158,7 +158,8 @@ class Trainer:
             # default on GPUs: all-gather / reduce-scatter fused into the GEMMs over peer memory
             # (--tp-transport nccl keeps the NCCL collectives); the arena is sized at the first step
             tp = TensorParallel(self.groups.tp_group, par.tp, self.tp_rank, self.device,
-                                use_p2p=train_cfg.extra.get("tp_transport", "p2p") == "p2p",
+                                use_p2p=train_cfg.extra.get("tp_transport", "p2p") in ("p2p", "p2p-tile"),
+                                tile_loads=train_cfg.extra.get("tp_transport", "p2p") == "p2p-tile",
                                 max_rows_local=int(train_cfg.extra.get("tp_max_rows_local", 0)),
                                 max_cols=max(model_cfg.hidden, 0))
         grad_dtype = {"bf16": None, "fp32": torch.float32}[train_cfg.grad_dtype]

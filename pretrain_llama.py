@@ -88,8 +88,10 @@ def parse_args(argv=None):
                     help="percp: no core-attention disaggregation; the data-parallel ranks form a per-document "
                          "context-parallel group instead (every document cut over all of them, K/V all-gathered, "
                          "dK/dV reduce-scattered with NCCL): the comparison point of the reference's --mode wlbllm")
-    ap.add_argument("--tp-transport", default="p2p", choices=["p2p", "nccl"],
-                    help="tensor-parallel all-gather / reduce-scatter: fused into the GEMMs over peer memory, or NCCL")
+    ap.add_argument("--tp-transport", default="p2p", choices=["p2p", "p2p-tile", "nccl"],
+                    help="tensor-parallel collectives: p2p = shards gathered once by peer stores + reduce-scatter in the "
+                         "GEMM epilogue; p2p-tile = all-gather in the GEMM's operand load as well (every CTA loads the "
+                         "remote tiles it needs); nccl = NCCL collectives")
     ap.add_argument("--dp-transport", default="p2p", choices=["p2p", "nccl"],
                     help="gradient reduce-scatter / parameter all-gather: fused kernels over peer memory, or NCCL")
     ap.add_argument("--attention-policy", default="cad", choices=["cad", "cp", "water_fill"],

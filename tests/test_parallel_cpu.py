@@ -26,7 +26,35 @@ def _free_port():
     return p
 
 
-def _worker(rank, world, port, tp, dp, q):
+class _GlooPeerCollectives:
+    """CPU stand-in for :class:`distca_b200.parallel.tp_p2p.PeerCollectives` (same methods, gloo collectives), so
+    that the model's peer-transport branches (shards gathered once, reduce-scatter taken by the GEMM) run
+    without a GPU."""
+
+    def __init__(self, group, size, rank, tile_loads=False):
+        self.group, self.size, self.rank, self.tile_loads = group, size, rank, tile_loads
+        self.max_rows, self.gathers, self.releases, self.rs_calls = 1 << 30, 0, 0, 0
+
+    def all_gather_rows(self, x):
+        assert self.gathers == self.releases, "the previous gather was not released"
+        self.gathers += 1
+        parts = [torch.empty_like(x) for _ in range(self.size)]
+        dist.all_gather(parts, x.contiguous(), group=self.group)
+        return torch.cat(parts)
+
+    def release_gather(self):
+        self.releases += 1
+
+    def linear_rs(self, x, w, residual=None, transposed_weight=False):
+        self.rs_calls += 1
+        y = x @ (w if transposed_weight else w.t())
+        dist.all_reduce(y, group=self.group)
+        n = y.shape[0] // self.size
+        out = y[self.rank * n:(self.rank + 1) * n].clone()
+        return out + residual if residual is not None else out
+
+
+def _worker(rank, world, port, tp, dp, q, peer_branches=False):
     try:
         os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port), RANK=str(rank), WORLD_SIZE=str(world),
                           LOCAL_RANK=str(rank))
@@ -38,7 +66,10 @@ def _worker(rank, world, port, tp, dp, q):
         full = {n: t.clone() for n, t in full_model.store.p.items()}
         tr = Trainer(CFG, par, TrainConfig(cad=False, recompute="full", lm_head_chunk=64, lr=1e-2), device="cpu", seed=3)
         tr.model.load_full_state(full)
-        src = BatchSource(CFG, par, 128, "loguniform64", seed=5, pinned=False)
+        fake = None
+        if peer_branches:
+            fake = tr.model.tp.fused = _GlooPeerCollectives(tr.groups.tp_group, tp, tr.tp_rank)
+        src = BatchSource(CFG, par, 256 if peer_branches else 128, "loguniform64", seed=5, pinned=False)
         hb = src.next(tr.dp_rank)
         tr.model.store.zero_grad()
         batch = tr.to_device(hb)
@@ -57,6 +88,9 @@ def _worker(rank, world, port, tp, dp, q):
             err = (tr.model.store.g[n] - want).abs().max().item()
             worst = max(worst, err / (want.abs().max().item() + 1e-9))
         ok = ok and worst < 1e-3
+        if fake is not None:
+            # per layer: 2 gathers forward, 2 in the recompute pass (the first layer is kept), 4 backward; 2 + 2 + 2 RS
+            ok = ok and fake.gathers == fake.releases > 0 and fake.rs_calls > 0 and tr.model.tp.nccl_row_collectives < 12
         # one optimizer step must leave every data-parallel replica with identical parameters
         tr.opt.step()
         flat = tr.model.store.flat.clone()
@@ -74,13 +108,15 @@ def _worker(rank, world, port, tp, dp, q):
         q.put((rank, False, repr(e), traceback.format_exc(), 0.0))
 
 
-@pytest.mark.parametrize("tp,dp", [(2, 1), (1, 2), (2, 2)])
-def test_tp_sp_dp_gradients(tp, dp):
+@pytest.mark.parametrize("tp,dp,peer_branches", [(2, 1, False), (1, 2, False), (2, 2, False), (2, 1, True)])
+def test_tp_sp_dp_gradients(tp, dp, peer_branches):
+    """``peer_branches``: the layer code paths of the peer tensor-parallel transport (gather once + local GEMM,
+    reduce-scatter taken over by the GEMM, forward / recompute / backward) with a gloo stand-in for the transport."""
     world = tp * dp
     ctx = mp.get_context("spawn")
     q = ctx.Queue()
     port = _free_port()
-    procs = [ctx.Process(target=_worker, args=(r, world, port, tp, dp, q)) for r in range(world)]
+    procs = [ctx.Process(target=_worker, args=(r, world, port, tp, dp, q, peer_branches)) for r in range(world)]
     for p in procs:
         p.start()
     results = [q.get(timeout=300) for _ in range(world)]
