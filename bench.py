@@ -308,6 +308,15 @@ def main() -> None:
     if a.config != "headline":
         run_named_config(a)
         return
+    if a.baseline_mode == "percp":
+        # the headline layout (one 128K pack per GPU) under per-document context parallelism instead of CAD:
+        # the like-for-like arm of the two attention schemes (same documents, same GPUs, TP = PP = 1)
+        NAMED_CONFIGS["headline_layout"] = {
+            "what": "headline layout", "model": a.model, "tp": 1, "pp": 1, "dp": a.gpus, "seq_len": a.seq_len or 131072,
+            "seqs_per_rank": 1, "microbatches": 1, "dist": a.dist, "recompute": a.recompute or "keep_attn"}
+        a.config = "headline_layout"
+        run_named_config(a)
+        return
     import torch
     import torch.distributed as dist
     from distca_b200.models.config import ParallelConfig, TrainConfig, get_model_config
