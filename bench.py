@@ -454,18 +454,23 @@ def main() -> None:
             if os.path.exists(pk):
                 with open(pk) as f:
                     mp = json.load(f)
-                peaks.update(bf16_tflops=mp["bf16_tflops_sustained"], hbm_gbs=mp["hbm_gbs"], source="measured (sustained GEMM)")
-            sb = trainer.cad.plan_stats.get("send_bytes", [0] * world)
-            remote = float(sum(sb) - sb[trainer.cad.me])
-            q_share = cfg.q_dim / (cfg.q_dim + 2.0 * cfg.kv_dim)        # the return trip carries O (forward) / dQ + copies (backward)
-            nparam = trainer.model.store.numel
-            gb = trainer.model.store.grad.element_size()
-            out["roofline"] = {"peaks": peaks, "paths": fused_path_rooflines(
-                phases, a.steps, tokens_per_rank=a.seq_len, hidden=cfg.hidden, qkv_dim=cfg.qkv_dim, layers=cfg.num_layers,
-                passes_qkv=2, attn_flops_fwd_per_rank=attn_flop / 3.0 / a.steps / world, remote_dispatch_bytes=remote,
-                remote_return_bytes=remote * q_share, grad_bytes_in=nparam * gb * (world - 1) / world,
-                param_bytes_out=nparam * 2 * (world - 1) / world,
-                optimizer_hbm_bytes=nparam / world * (gb * world + 2 + 2 + 16 + 2 * world), peaks=peaks)}
+                if "bf16_tflops_sustained" in mp and "hbm_gbs" in mp:
+                    peaks.update(bf16_tflops=mp["bf16_tflops_sustained"], hbm_gbs=mp["hbm_gbs"],
+                                 source="measured (sustained GEMM)")
+            try:
+                sb = list(trainer.cad.plan_stats.get("send_bytes", [0] * world))
+                remote = float(sum(sb) - (sb[trainer.cad.me] if trainer.cad.me < len(sb) else 0))
+                q_share = cfg.q_dim / (cfg.q_dim + 2.0 * cfg.kv_dim)    # the return trip carries O (forward) / dQ + copies (backward)
+                nparam = trainer.model.store.numel
+                gb = trainer.model.store.grad.element_size()
+                out["roofline"] = {"peaks": peaks, "paths": fused_path_rooflines(
+                    phases, a.steps, tokens_per_rank=a.seq_len, hidden=cfg.hidden, qkv_dim=cfg.qkv_dim, layers=cfg.num_layers,
+                    passes_qkv=2, attn_flops_fwd_per_rank=attn_flop / 3.0 / a.steps / world, remote_dispatch_bytes=remote,
+                    remote_return_bytes=remote * q_share, grad_bytes_in=nparam * gb * (world - 1) / world,
+                    param_bytes_out=nparam * 2 * (world - 1) / world,
+                    optimizer_hbm_bytes=nparam / world * (gb * world + 2 + 2 + 16 + 2 * world), peaks=peaks)}
+            except Exception as e:   # a diagnostic block must never cost the measurement its output line
+                out["roofline"] = {"peaks": peaks, "error": repr(e)}
             out["cad"] = {"planned_imbalance_after": trainer.cad.plan_stats.get("imbalance_after"),
                           "planned_imbalance_before": trainer.cad.plan_stats.get("imbalance_before"),
                           "planned_cost_imbalance_after": trainer.cad.plan_stats.get("cost_imbalance_after"),

@@ -192,3 +192,33 @@ def test_layout_search_enumerates_every_factorisation_and_prefers_disaggregation
             assert r["step_ms_cad"] <= r["step_ms_local_attention"] * 1.02
         else:
             assert r["step_ms_cad"] == r["step_ms_local_attention"]       # one server: nothing to disaggregate
+
+
+def test_fused_path_rooflines_name_the_binding_resource_of_every_path():
+    """The bench line's roofline block: per path the slower of FLOPs at the GEMM peak, bytes over NVLink and bytes
+    through HBM, against the measured phase time; a path whose phase was not timed reports no fraction."""
+    from distca_b200.utils.observability import fused_path_rooflines
+    peaks = {"bf16_tflops": 1400.0, "hbm_gbs": 6455.0, "link_gbs": 770.0, "source": "test"}
+    steps, layers, T, H, QKV = 2, 32, 131072, 4096, 6144
+    phases = {"gemm_qkv": 2 * 400.0, "re_gemm_qkv": 2 * 400.0, "cad_attn_fwd": 2 * 3000.0, "cad_attn_bwd": 2 * 8000.0,
+              "optimizer": 2 * 60.0}
+    attn_fwd = 2.7e15
+    r = fused_path_rooflines(phases, steps, tokens_per_rank=T, hidden=H, qkv_dim=QKV, layers=layers, passes_qkv=2,
+                             attn_flops_fwd_per_rank=attn_fwd, remote_dispatch_bytes=1.0e9, remote_return_bytes=0.67e9,
+                             grad_bytes_in=8e9 * 2 * 7 / 8, param_bytes_out=8e9 * 2 * 7 / 8,
+                             optimizer_hbm_bytes=1e9 * (2 * 8 + 20 + 16), peaks=peaks)
+    assert set(r) == {"qkv_gemm_rope_dispatch", "attention_forward_with_output_return",
+                      "attention_backward_with_gradient_return", "gradient_reduce_scatter_adam_all_gather"}
+    q = r["qkv_gemm_rope_dispatch"]
+    flops_ms = 2.0 * T * H * QKV * layers * 2 / 1400e12 * 1e3
+    link_ms = 1.0e9 * layers * 2 / 770e9 * 1e3
+    assert q["ms"] == 800.0 and q["bound"] == ("tensor" if flops_ms > link_ms else "nvlink")
+    assert abs(q["roofline_ms"] - max(flops_ms, link_ms)) < 0.01
+    assert 0 < q["fraction_of_roofline"] <= 1.0
+    assert r["attention_forward_with_output_return"]["bound"] == "tensor"
+    assert r["gradient_reduce_scatter_adam_all_gather"]["bound"] == "nvlink"
+    # nothing timed (timers off, one GPU): no division by zero, no fraction
+    empty = fused_path_rooflines({}, 1, tokens_per_rank=T, hidden=H, qkv_dim=QKV, layers=layers, passes_qkv=2,
+                                 attn_flops_fwd_per_rank=0.0, remote_dispatch_bytes=0.0, remote_return_bytes=0.0,
+                                 grad_bytes_in=0.0, param_bytes_out=0.0, optimizer_hbm_bytes=0.0, peaks=peaks)
+    assert all(v["fraction_of_roofline"] is None for v in empty.values())

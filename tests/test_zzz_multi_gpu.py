@@ -96,3 +96,12 @@ def test_cad_dp2_pingpong_two_streams():
     both accumulate into the same buffers (ordered by events)."""
     res = _run(2, 29550, ["--tokens", "8192", "--nano", "2", "--recompute", "keep_attn"])
     assert res["ok"], res
+
+
+@pytest.mark.skipif(_ngpu() < 2, reason="needs 2 GPUs")
+def test_documents_spanning_ranks_train_like_the_per_document_cp_baseline():
+    """--span-documents: one global batch laid out over the ranks by the planner (documents longer than a rank's
+    share are held as head / tail pieces by several ranks) with core-attention disaggregation, against the
+    per-document CP baseline on the same global batches."""
+    res = _run(2, 29551, ["--tokens", "4096", "--steps", "3"], check="span")
+    assert res["ok"] and res["longest_document"] > res["tokens_per_rank"] // 2, res
