@@ -38,6 +38,8 @@ Reference counterparts: dispatch/all-to-all/unpack autograd ops (distca/runtime/
 """
 from __future__ import annotations
 
+import os
+
 import numpy as np
 import torch
 
@@ -84,7 +86,13 @@ class CadRuntime:
         self._pending_speed = None
         self.speed = None                   # relative speed per server after the last feedback
         self._attn_events: list = []        # (start, end) CUDA events of this step's attention calls
-        self._wait_events: list = []        # ... and of its signal waits (time this rank stood idle)
+        self._wait_events: list = []        # ... and of its signal waits (time this rank stood idle), with the wait's name
+        # waits longer than this many milliseconds are kept as "blocking events" (the reference's TickSync blocking
+        # detection, distca/runtime/megatron/ops/stream_sync_fn.py:24-77); None: off
+        thr = train_cfg.extra.get("wait_report_ms", os.environ.get("DISTCA_WAIT_REPORT_MS"))
+        self.wait_report_ms = float(thr) if thr not in (None, "") else None
+        self.blocking_events: list = []     # dicts {step, wait, index, ms}, newest last, at most 4096 kept
+        self._steps_seen = 0
         self._predicted_ms = 0.0            # what the cost model predicted for them
         self.predicted_ms = 0.0             # cost-model milliseconds (forward + backward) of the current plan on this server
 
@@ -264,8 +272,9 @@ class CadRuntime:
                 return False
         return _T()
 
-    def _timed_wait(self):
-        """Context manager: CUDA events around one signal wait (how long this rank stood idle)."""
+    def _timed_wait(self, what: str = ""):
+        """Context manager: CUDA events around one signal wait (how long this rank stood idle). ``what`` names the
+        wait in the blocking report."""
         rt = self
 
         class _T:
@@ -279,7 +288,7 @@ class CadRuntime:
                 if rt.speed_feedback and rt.use_cost_model:
                     b = torch.cuda.Event(enable_timing=True)
                     b.record()
-                    rt._wait_events.append((self_inner.a, b))
+                    rt._wait_events.append((self_inner.a, b, what))
                 return False
         return _T()
 
@@ -295,7 +304,12 @@ class CadRuntime:
         if not (self.speed_feedback and self.use_cost_model) or self.arena is None:
             return
         measured = sum(a.elapsed_time(b) for a, b in self._attn_events)
-        waited = sum(a.elapsed_time(b) for a, b in self._wait_events)
+        waits = [(w, a.elapsed_time(b)) for a, b, w in self._wait_events]
+        waited = sum(ms for _, ms in waits)
+        self._steps_seen += 1
+        if self.wait_report_ms is not None:
+            self.blocking_events = (self.blocking_events
+                                    + self.blocking_report(waits, self.wait_report_ms, self._steps_seen))[-4096:]
         predicted, self._attn_events, self._wait_events, self._predicted_ms = self._predicted_ms, [], [], 0.0
         import torch.distributed as dist
         mine = torch.tensor([measured, predicted, waited], dtype=torch.float32, device=self.device)
@@ -320,6 +334,21 @@ class CadRuntime:
     # ------------------------------------------------------------------------------------------
     # server halves (every rank of the group runs them once per layer and direction)
     @staticmethod
+    def blocking_report(waits, threshold_ms: float, step: int = 0) -> list:
+        """``waits``: (name, milliseconds) of one step's signal waits in launch order. Returns one record per wait
+        that kept the stream idle for longer than ``threshold_ms``: which wait, its index among the step's waits of
+        that name (= the layer, in forward order for the forward waits and in backward order for the others) and
+        how long."""
+        seen: dict = {}
+        out = []
+        for name, ms in waits:
+            k = seen.get(name, 0)
+            seen[name] = k + 1
+            if ms > threshold_ms:
+                out.append({"step": step, "wait": name, "index": k, "ms": round(float(ms), 3)})
+        return out
+
+    @staticmethod
     def feedback_shares(attn_ms, predicted, idle_ms, wait_gain: float = 0.5):
         """Relative share of the attention work per server (mean 1) from one step's measurements."""
         attn_ms, predicted, idle_ms = (np.asarray(x, dtype=np.float64) for x in (attn_ms, predicted, idle_ms))
@@ -334,7 +363,7 @@ class CadRuntime:
         self._serve_forward_end()
 
     def _serve_forward_begin(self) -> None:
-        with timers.phase("cad_wait_qkv"), self._timed_wait():
+        with timers.phase("cad_wait_qkv"), self._timed_wait("qkv"):
             self.sig.wait(SIG_QKV)
         with timers.phase("cad_attn_fwd"), self._timed_attention(self._FWD_SHARE):
             attn_ops.flash_fwd(self.Qr, self.Kr, self.Vr, self.attn_plan, out=self.AO.unflatten(1, (self.hq, self.D)),
@@ -342,7 +371,7 @@ class CadRuntime:
         self.sig.signal(SIG_OUT)
 
     def _serve_forward_end(self) -> None:
-        with timers.phase("cad_wait_out"), self._timed_wait():
+        with timers.phase("cad_wait_out"), self._timed_wait("out"):
             self.sig.wait(SIG_OUT)
 
     def _serve_backward(self, layer: int | None = None) -> None:
@@ -350,7 +379,7 @@ class CadRuntime:
         self._serve_backward_end()
 
     def _serve_backward_begin(self, layer: int | None = None) -> None:
-        with timers.phase("cad_wait_dout"), self._timed_wait():
+        with timers.phase("cad_wait_dout"), self._timed_wait("dout"):
             self.sig.wait(SIG_DOUT)   # also covers this layer's Q/K/V rows: every owner sends them first
         nq, nk = max(self.q_rows, 1), max(self.kv_rows, 1)
         lse = self.LSE[:nq]    # sent by the owners together with dO and delta
@@ -379,7 +408,7 @@ class CadRuntime:
             self.sig.signal(SIG_DQKV)
 
     def _serve_backward_end(self) -> None:
-        with timers.phase("cad_wait_dqkv"), self._timed_wait():
+        with timers.phase("cad_wait_dqkv"), self._timed_wait("dqkv"):
             self.sig.wait(SIG_DQKV)
 
     # ------------------------------------------------------------------------------------------

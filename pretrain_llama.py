@@ -110,6 +110,10 @@ def parse_args(argv=None):
     ap.add_argument("--grad-dtype", default="bf16", choices=["bf16", "fp32"])
     ap.add_argument("--log-memory", action="store_true", default=os.environ.get("EXPERIMENT_LOG_MEMORY_USAGE", "0") == "1")
     ap.add_argument("--phase-timers", action="store_true")
+    ap.add_argument("--wait-report-ms", type=float, default=(float(os.environ["DISTCA_WAIT_REPORT_MS"])
+                                                              if os.environ.get("DISTCA_WAIT_REPORT_MS") else None),
+                    help="record every signal wait of the attention servers that kept the stream idle for longer than "
+                         "this many milliseconds (which wait, which layer, how long) in the step records")
     ap.add_argument("--nvtx", action="store_true", help="NVTX ranges per step, tick, layer pass and phase")
     return ap.parse_args(argv)
 
@@ -144,6 +148,8 @@ def main(argv=None) -> int:
     tc.extra["baseline_mode"] = a.baseline_mode
     tc.extra["tp_transport"] = a.tp_transport
     tc.extra["dp_transport"] = a.dp_transport
+    if a.wait_report_ms is not None:
+        tc.extra["wait_report_ms"] = a.wait_report_ms
     if a.baseline_mode == "percp" and a.pp_size > 1:
         raise SystemExit("--baseline-mode percp has no pipeline stages: use --pp-size 1")
     tc.extra["nano_batches"] = 2 if (a.pingpong and cad and a.pp_size == 1 and world > 1 and not a.span_documents) else 1   # ping-pong nano-batches (non-pipelined trainer)
@@ -230,6 +236,8 @@ def main(argv=None) -> int:
             ph = timers.GLOBAL.summary(reset=not a.phase_timers) if timers.GLOBAL.enabled else {}
             rec["exposed_dispatch_ms"] = (sum(v for k, v in ph.items() if k.removeprefix("re_").startswith("cad_wait") or
                                               k.removeprefix("re_") in ("cad_dispatch", "cad_return")) if ph else None)
+            if cad_rt.wait_report_ms is not None:
+                rec["blocking_waits"] = [e for e in cad_rt.blocking_events if e["step"] == cad_rt._steps_seen]
             if cad_rt.last_plan is not None:
                 art.plan({"step": it, **inspect_plan(cad_rt.last_plan, cad_rt.W)})
         if a.phase_timers:

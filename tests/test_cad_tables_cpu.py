@@ -149,3 +149,14 @@ def test_feedback_shares_move_work_towards_idle_servers():
     slow_attention = CadRuntime.feedback_shares([100, 100, 100, 125], [100] * 4, [20, 20, 20, 0])
     assert slow_attention[3] < slow_gemms[3]
     assert np.all(CadRuntime.feedback_shares([1, 1, 1, 100], [1] * 4, [0] * 4) >= 0.75)      # bounded
+
+
+def test_blocking_report_names_the_waits_that_kept_the_stream_idle():
+    """The wait report (the reference's TickSync blocking detection): one record per signal wait above the
+    threshold, with the wait's name and its index among the step's waits of that name (the layer)."""
+    from distca_b200.parallel.cad import CadRuntime
+    waits = [("qkv", 0.02), ("out", 0.4), ("qkv", 3.5), ("out", 0.1), ("dout", 1.2), ("dqkv", 0.0), ("dout", 0.9)]
+    rep = CadRuntime.blocking_report(waits, threshold_ms=1.0, step=7)
+    assert rep == [{"step": 7, "wait": "qkv", "index": 1, "ms": 3.5}, {"step": 7, "wait": "dout", "index": 0, "ms": 1.2}]
+    assert CadRuntime.blocking_report(waits, threshold_ms=10.0) == []
+    assert CadRuntime.blocking_report([], threshold_ms=0.0) == []
