@@ -236,7 +236,7 @@ def main(argv=None) -> int:
             ph = timers.GLOBAL.summary(reset=not a.phase_timers) if timers.GLOBAL.enabled else {}
             rec["exposed_dispatch_ms"] = (sum(v for k, v in ph.items() if k.removeprefix("re_").startswith("cad_wait") or
                                               k.removeprefix("re_") in ("cad_dispatch", "cad_return")) if ph else None)
-            if cad_rt.wait_report_ms is not None:
+            if getattr(cad_rt, "wait_report_ms", None) is not None:
                 rec["blocking_waits"] = [e for e in cad_rt.blocking_events if e["step"] == cad_rt._steps_seen]
             if cad_rt.last_plan is not None:
                 art.plan({"step": it, **inspect_plan(cad_rt.last_plan, cad_rt.W)})
