@@ -76,8 +76,9 @@ def _args():
                     help="headline: the dp{N} + CAD scaling benchmark (default); the others are fixed 8-GPU layouts: "
                          + "; ".join(f"{k}: {v['what']}" for k, v in NAMED_CONFIGS.items()))
     ap.add_argument("--baseline-mode", default="none", choices=["none", "percp"],
-                    help="percp (with --config): the no-CAD per-document context-parallel baseline on the same documents "
-                         "(tensor parallel x context parallel over the remaining ranks, all-gather K/V)")
+                    help="percp: the no-CAD per-document context-parallel baseline on the same documents (all-gather K/V; "
+                         "with --config: tensor parallel x context parallel over the remaining ranks; on the headline "
+                         "layout: context parallel over all GPUs)")
     ap.add_argument("--microbatches", type=int, default=None, help="micro-batches per step of a pipelined --config")
     ap.add_argument("--phase-timers", action="store_true",
                     help="CUDA-event phase timers in the device-timed region; the JSON line gains phases_ms_per_step")

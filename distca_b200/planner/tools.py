@@ -80,18 +80,118 @@ def compare_policies(model: str, world: int, tokens: int, dist: str, iterations:
             "note": "wlb_packing leaves ranks with unequal token counts (linear layers unbalanced); not modelled here"}
 
 
+# Calibration of the step model against one measured Llama-3-8B step on one B200 (131072 tokens, long/short
+# mixture, keep_attn: CUDA-event phase timers, ms per step): GEMMs forward + recompute 2853, GEMMs backward 2784,
+# norms 63 + 59, SwiGLU backward 109, RoPE backward 21, LM head 422, attention forward 2848 / backward 8437,
+# optimizer and host 240.
+BWD_OVER_FWD_LINEAR = 2.0        # (2784 + 59 + 109 + 21) / forward linear time
+RECOMPUTE_OVER_FWD_LINEAR = 0.95  # the recompute pass skips the FC2 GEMM
+BWD_OVER_FWD_ATTENTION = 2.96    # 8437 / 2848: the backward kernels run at a lower fraction of peak
+ATTENTION_IN_STEP = 1.26         # the attention table was timed in isolation (burst clocks, 1.20 PFLOP/s at these lengths);
+                                 # inside a power-capped step the same kernel ran at 0.95 PFLOP/s
+LM_HEAD_MS_PER_TOKEN = 422.0 / 131072       # forward + backward, vocabulary 128256 x hidden 4096
+OPTIMIZER_MS_8B = 240.0          # sharded AdamW over 8.03e9 parameters on one GPU
+STORE_LINK_EFFICIENCY = 0.70     # peer stores from many CTAs against the measured peer copy (536 of 770 GB/s)
+TILE_LOAD_GBS = 300.0            # per-tile remote TMA loads (p2p-tile): coarse; the measured TP > 1 steps imply 135-570 GB/s
+
+
+def _tp_comm_ms(cfg, tok: int, tp: int, layers: float, link_bytes_per_ms: float, recompute: str, transport: str) -> float:
+    """Time of a tensor-parallel rank's all-gathers that is NOT hidden behind GEMMs, per step. ``gather``: every
+    shard pushed once, then a local GEMM (serial); ``tile``: the GEMM loads remote tiles itself and re-fetches a
+    tile once per N tile that uses it; ``nccl``: library collectives, all-gathers and reduce-scatters serial. The
+    reduce-scatters of the peer transports ride in GEMM epilogues."""
+    if tp == 1:
+        return 0.0
+    shard = tok * cfg.hidden * 2 * (tp - 1) / tp               # bytes one all-gather / reduce-scatter moves per rank
+    passes_ag = 2 + (2 if recompute != "none" else 0) + 4      # forward n1, n2; recompute n1, n2; backward dy, n2, dh, n1
+    passes_rs = 2 + (1 if recompute != "none" else 0) + 2
+    if transport == "nccl":
+        return (passes_ag + passes_rs) * shard / link_bytes_per_ms * layers
+    if transport == "gather":
+        return passes_ag * shard / (link_bytes_per_ms * STORE_LINK_EFFICIENCY) * layers
+    # per-tile loads: operand bytes x N tiles of the consuming GEMM (QKV, FC1 forward and recompute; dact, dattn backward)
+    nt = lambda n: max(1.0, n / tp / 256.0)
+    fwd = nt(cfg.qkv_dim) + nt(2 * cfg.ffn)
+    bwd = nt(cfg.ffn) + nt(cfg.q_dim)
+    tiles = fwd * (2 if recompute != "none" else 1) + bwd
+    gathers = 2                                                # n2, n1 for the weight gradients (pushed once)
+    return (tiles * shard / (TILE_LOAD_GBS * 1e6) + gathers * shard / (link_bytes_per_ms * STORE_LINK_EFFICIENCY)) * layers
+
+
+def predict_step_ms(cfg, tm, packs: list[list[int]], tokens: int, tp: int, pp: int, dp: int, microbatches: int,
+                    mode: str, recompute: str = "keep_attn", tp_transport: str = "gather",
+                    tolerance: float = 0.02) -> dict:
+    """Predicted milliseconds of one training step (forward, recompute, backward, optimizer) of the global batch
+    ``packs`` (document lengths per packed sequence, ``len(packs)`` a multiple of ``dp``) under one layout.
+    ``mode``: ``cad`` (core attention spread over the dp x pp servers by the planner), ``local`` (every rank attends
+    to its own documents) or ``percp`` (per-document context parallelism over the dp ranks, all-gathered K/V; no
+    pipeline stages). Returns the parts as well."""
+    L = cfg.num_layers
+    ref = get_model_config("llama3-8b")
+    per_rank_seqs = len(packs) // dp
+    per_rank = [sum(packs[r * per_rank_seqs:(r + 1) * per_rank_seqs], []) for r in range(dp)]
+    tok_rank = per_rank_seqs * tokens
+    link = tm.link_gbytes_per_s * 1e6                                  # bytes per ms
+    passes_lin = 1.0 + BWD_OVER_FWD_LINEAR + (RECOMPUTE_OVER_FWD_LINEAR if recompute != "none" else 0.0)
+    passes_attn = 1.0 + BWD_OVER_FWD_ATTENTION + (1.0 if recompute == "full" else 0.0)
+    scale_lin = cfg.flops_per_token_linear() / ref.flops_per_token_linear() * ref.num_layers / L   # per layer
+    lin = passes_lin * tm.linear_ms_per_token * scale_lin * tok_rank / tp * (L / pp)
+    lm = LM_HEAD_MS_PER_TOKEN * tok_rank / tp * (cfg.vocab * cfg.hidden) / (ref.vocab * ref.hidden)
+    opt = OPTIMIZER_MS_8B * (cfg.flops_per_token_linear() / ref.flops_per_token_linear()) / (tp * pp * dp)
+    tp_comm = _tp_comm_ms(cfg, tok_rank, tp, L / pp, link, recompute, tp_transport)
+    heads = ATTENTION_IN_STEP * cfg.heads_q / 32.0 / tp
+    whole = lambda n: tm.attn_ms_for(n, n)
+    disp = 0.0
+    if mode == "percp":
+        assert pp == 1, "the per-document CP baseline has no pipeline stages"
+        # every document cut into 2 x dp chunks, every rank holds a head and a tail chunk: 1 / dp of each document's
+        # pairs, but 2 query chunks per document and rank (short documents pay the per-tile cost dp times over)
+        docs = [x for d in per_rank for x in d]
+        attn_fwd = 0.0
+        for x in docs:
+            c = max(1, x // (2 * dp))
+            attn_fwd += max(whole(x) / dp, 2.0 * whole(min(c, 128)))   # at least two (partial) tiles of work per document
+        kv_bytes = sum(docs) * 2 * cfg.kv_dim / tp * 2 * (dp - 1) / dp  # K and V of every other rank, bf16
+        passes_kv = 1 + (1 if recompute != "none" else 0) + 1 + 1       # all-gather fwd, recompute, bwd; reduce-scatter dK/dV
+        disp = passes_kv * kv_bytes / link * L
+        attn = passes_attn * attn_fwd * heads * L
+        servers = dp
+    elif mode == "cad" and dp * pp > 1:
+        servers = dp * pp
+        p = Planner(PlannerConfig.for_model(cfg, servers, max(sum(d) for d in per_rank) or tokens, tp=tp, tolerance=tolerance))
+        # every pipeline stage serves: the data-parallel ranks' documents are spread over dp x pp servers
+        plan = p.plan_fixed([per_rank[r % dp] if r < dp else [] for r in range(servers)])
+        sim = p.simulate(plan, tm)
+        # the plan spreads ONE layer's attention of all sequences in flight over dp x pp servers; every server
+        # serves all L layers (its own stage's layers for pp different micro-batches)
+        attn = passes_attn * max(sim.attn_ms) * heads * L
+        disp = (4 if recompute != "none" else 3) * max(sim.comm_ms) / tp * L
+    else:
+        attn = passes_attn * max(sum(whole(x) for x in d) for d in per_rank) * heads * (L / pp)
+    bubble = (pp - 1) / (microbatches + pp - 1) if pp > 1 else 0.0
+    busy = lin + tp_comm + lm
+    if mode == "cad" and dp * pp > 1 and pp > 1:
+        # idle pipeline slots serve attention: the servers' attention work fills the bubble first
+        step = busy + max(busy * bubble / (1.0 - bubble), attn + disp)
+    else:
+        stage = busy + attn + disp
+        step = stage / (1.0 - bubble) if pp > 1 else stage
+    return {"step_ms": step + opt, "linear_ms": lin, "lm_head_ms": lm, "tp_comm_ms": tp_comm, "attention_ms": attn,
+            "dispatch_ms": disp, "optimizer_ms": opt, "bubble_fraction": bubble}
+
+
 def search_layouts(model: str, gpus: int, tokens: int, dist: str, iterations: int = 10, tolerance: float = 0.02,
-                   seed: int = 0, microbatches: int | None = None, seqs_per_step: int | None = None) -> dict:
-    """Simulated milliseconds per step (forward + backward = 3 x forward linear, 3.3 x forward attention) of a
-    fixed global batch of ``seqs_per_step`` packed sequences (default: one per GPU) under every layout."""
+                   seed: int = 0, microbatches: int | None = None, seqs_per_step: int | None = None,
+                   recompute: str = "keep_attn", tp_transport: str = "gather") -> dict:
+    """Predicted milliseconds per training step of a fixed global batch of ``seqs_per_step`` packed sequences
+    (default: one per GPU) under every (tp, pp, dp) layout of ``gpus`` GPUs, with local attention, with core-attention
+    disaggregation and (layouts without pipeline stages) with the per-document CP baseline."""
     cfg = get_model_config(model)
     tm = default_time_model("b200")
     seqs = seqs_per_step or gpus
     src = SyntheticBatches(tokens, seqs, dist, seed)
     batches = [src.next_doc_lens() for _ in range(iterations)]
     L = cfg.num_layers
-    link = tm.link_gbytes_per_s * 1e6            # bytes per ms
-    scale_lin = cfg.flops_per_token_linear() / get_model_config("llama3-8b").flops_per_token_linear() * 32 / L
     rows = []
     for tp in (t for t in (1, 2, 4, 8) if gpus % t == 0 and cfg.heads_kv % t == 0):
         for pp in (p for p in (1, 2, 4) if (gpus // tp) % p == 0 and L % p == 0):
@@ -101,47 +201,20 @@ def search_layouts(model: str, gpus: int, tokens: int, dist: str, iterations: in
             M = microbatches or max(pp, seqs // dp)
             if (seqs // dp) % M and pp > 1:
                 continue
-            per_rank_seqs = seqs // dp                       # sequences a data-parallel rank sees per step
             res = {}
-            for cad in (False, True):
-                tot = 0.0
-                for packs in batches:
-                    per_rank = [sum(packs[r * per_rank_seqs:(r + 1) * per_rank_seqs], []) for r in range(dp)]
-                    tok_rank = per_rank_seqs * tokens
-                    lin = 3.0 * tm.linear_ms_per_token * scale_lin * tok_rank / tp * (L / pp)
-                    # tensor-parallel collectives: 4 all-gathers / reduce-scatters of [tokens, hidden] per layer pass, x3 passes
-                    tp_comm = 0.0 if tp == 1 else 3 * 4 * (tok_rank * cfg.hidden * 2 * (tp - 1) / tp) / link * (L / pp)
-                    servers = dp * pp
-                    if cad and servers > 1:
-                        p = Planner(PlannerConfig.for_model(cfg, servers, max(sum(d) for d in per_rank) or tokens, tp=tp,
-                                                            tolerance=tolerance))
-                        # every pipeline stage serves: spread the data-parallel ranks' documents over dp x pp servers
-                        docs = [per_rank[r % dp] if r < dp else [] for r in range(servers)]
-                        plan = p.plan_fixed(docs)
-                        sim = p.simulate(plan, tm)
-                        # the plan spreads ONE layer's attention of all sequences in flight over dp x pp servers; every
-                        # server serves all L layers (its own stage's layers for pp different micro-batches)
-                        attn = 3.3 * max(sim.attn_ms) * cfg.heads_q / 32 / tp * L
-                        disp = 4 * max(sim.comm_ms) / tp * L
-                    else:
-                        whole = lambda n: tm.attn_ms_for(n, n)
-                        attn = 3.3 * max(sum(whole(x) for x in d) for d in per_rank) * cfg.heads_q / 32 / tp * (L / pp)
-                        disp = 0.0
-                    bubble = (pp - 1) / (M + pp - 1) if pp > 1 else 0.0
-                    if cad and servers > 1 and pp > 1:
-                        # idle pipeline slots serve attention: the servers' attention work fills the bubble first
-                        busy = lin + tp_comm
-                        tot += busy + max(busy * bubble / (1.0 - bubble), attn + disp)
-                    else:
-                        stage = lin + tp_comm + attn + disp
-                        tot += stage / (1.0 - bubble) if pp > 1 else stage
-                res["cad" if cad else "local"] = tot / len(batches)
-            rows.append({"tp": tp, "pp": pp, "dp": dp, "microbatches": M if pp > 1 else 1,
-                         "step_ms_local_attention": round(res["local"], 1), "step_ms_cad": round(res["cad"], 1)})
+            for mode in ("local", "cad") + (("percp",) if pp == 1 and dp > 1 else ()):
+                res[mode] = float(np.mean([predict_step_ms(cfg, tm, packs, tokens, tp, pp, dp, M, mode, recompute,
+                                                           tp_transport, tolerance)["step_ms"] for packs in batches]))
+            row = {"tp": tp, "pp": pp, "dp": dp, "microbatches": M if pp > 1 else 1,
+                   "step_ms_local_attention": round(res["local"], 1), "step_ms_cad": round(res["cad"], 1)}
+            if "percp" in res:
+                row["step_ms_percp"] = round(res["percp"], 1)
+            rows.append(row)
     rows.sort(key=lambda r: min(r["step_ms_local_attention"], r["step_ms_cad"]))
     return {"model": cfg.name, "gpus": gpus, "tokens_per_sequence": tokens, "sequences_per_step": seqs, "dist": dist,
-            "layouts": rows, "note": "simulated from the attention table, the per-token linear time and the link "
-                                     "bandwidth of the B200 time model; memory limits are not checked here"}
+            "recompute": recompute, "tp_transport": tp_transport, "layouts": rows,
+            "note": "predicted from the attention table, the per-token linear time and the link bandwidth of the B200 "
+                    "time model, calibrated on one measured step; memory limits are not checked here"}
 
 
 def main() -> None:
@@ -153,8 +226,18 @@ def main() -> None:
     ap.add_argument("--dist", default="mixture")
     ap.add_argument("--iterations", type=int, default=20)
     ap.add_argument("--tolerance", type=float, default=0.02)
+    ap.add_argument("--seqs-per-step", type=int, default=None, help="layouts: packed sequences per step (default: one per GPU)")
+    ap.add_argument("--microbatches", type=int, default=None, help="layouts: micro-batches per step of the pipelined layouts")
+    ap.add_argument("--recompute", default="keep_attn", choices=["none", "full", "keep_attn"])
+    ap.add_argument("--tp-transport", default="gather", choices=["gather", "tile", "nccl"],
+                    help="layouts: how a tensor-parallel all-gather reaches its GEMM (gather = --tp-transport p2p)")
     a = ap.parse_args()
-    f = {"buffer": recommend_buffer_gb, "compare": compare_policies, "layouts": search_layouts}[a.tool]
+    if a.tool == "layouts":
+        print(json.dumps(search_layouts(a.model, a.world, a.tokens, a.dist, a.iterations, a.tolerance,
+                                        microbatches=a.microbatches, seqs_per_step=a.seqs_per_step,
+                                        recompute=a.recompute, tp_transport=a.tp_transport)))
+        return
+    f = {"buffer": recommend_buffer_gb, "compare": compare_policies}[a.tool]
     print(json.dumps(f(a.model, a.world, a.tokens, a.dist, a.iterations, a.tolerance)))
 
 

@@ -222,3 +222,35 @@ def test_fused_path_rooflines_name_the_binding_resource_of_every_path():
                                  attn_flops_fwd_per_rank=0.0, remote_dispatch_bytes=0.0, remote_return_bytes=0.0,
                                  grad_bytes_in=0.0, param_bytes_out=0.0, optimizer_hbm_bytes=0.0, peaks=peaks)
     assert all(v["fraction_of_roofline"] is None for v in empty.values())
+
+
+def test_step_model_reproduces_the_measured_one_gpu_step_and_orders_the_tensor_parallel_transports():
+    """``predict_step_ms`` is calibrated on one measured Llama-3-8B step (one B200, 131072 tokens, keep_attn:
+    17.67 s with 5.9 s of linear layers). Its parts must add up to that for such a batch, the per-tile transport
+    must cost more than gather-once (a remote tile is fetched once per N tile), and the per-document CP arm exists
+    exactly for the layouts without pipeline stages."""
+    from distca_b200.data.synthetic import SyntheticBatches
+    from distca_b200.models.config import get_model_config
+    from distca_b200.planner import default_time_model
+    from distca_b200.planner.tools import predict_step_ms, search_layouts
+    cfg, tm = get_model_config("llama3-8b"), default_time_model("b200")
+    src = SyntheticBatches(131072, 1, "mixture", 0)
+    steps = [predict_step_ms(cfg, tm, src.next_doc_lens(), 131072, 1, 1, 1, 1, "local") for _ in range(10)]
+    lin = steps[0]["linear_ms"]
+    assert abs(lin - 5889.0) / 5889.0 < 0.03                      # measured: 2853 + 2784 + norms, SwiGLU, RoPE backward
+    mean = sum(s["step_ms"] for s in steps) / len(steps)
+    assert 0.8 * 17669 < mean < 1.2 * 17669, mean                # the attention share moves with the documents drawn
+    for s in steps:
+        parts = s["linear_ms"] + s["lm_head_ms"] + s["tp_comm_ms"] + s["attention_ms"] + s["dispatch_ms"] + s["optimizer_ms"]
+        assert abs(parts - s["step_ms"]) < 1e-6
+    packs = SyntheticBatches(131072, 4, "mixture", 1).next_doc_lens()
+    t = {tr: predict_step_ms(cfg, tm, packs, 131072, 2, 1, 4, 1, "cad", tp_transport=tr) for tr in ("gather", "nccl", "tile")}
+    assert t["gather"]["tp_comm_ms"] < t["nccl"]["tp_comm_ms"] < t["tile"]["tp_comm_ms"]
+    assert t["tile"]["tp_comm_ms"] > 10 * t["gather"]["tp_comm_ms"]
+    full = predict_step_ms(cfg, tm, packs, 131072, 1, 1, 4, 1, "cad", recompute="full")
+    keep = predict_step_ms(cfg, tm, packs, 131072, 1, 1, 4, 1, "cad", recompute="keep_attn")
+    none = predict_step_ms(cfg, tm, packs, 131072, 1, 1, 4, 1, "cad", recompute="none")
+    assert full["attention_ms"] > keep["attention_ms"] == none["attention_ms"] and keep["linear_ms"] > none["linear_ms"]
+    res = search_layouts("llama3-8b", 8, 32768, "mixture", iterations=1)
+    for r in res["layouts"]:
+        assert ("step_ms_percp" in r) == (r["pp"] == 1 and r["dp"] > 1)
