@@ -313,9 +313,9 @@ class CadRuntime:
         predicted, self._attn_events, self._wait_events, self._predicted_ms = self._predicted_ms, [], [], 0.0
         import torch.distributed as dist
         mine = torch.tensor([measured, predicted, waited], dtype=torch.float32, device=self.device)
-        allv = torch.empty(self.W, 3, dtype=torch.float32, device=self.device)
+        allv = torch.empty(self.W * 3, dtype=torch.float32, device=self.device)
         dist.all_gather_into_tensor(allv, mine, group=self.group)
-        allv = allv.cpu().numpy().astype(np.float64)
+        allv = allv.view(self.W, 3).cpu().numpy().astype(np.float64)
         if (allv[:, :2] <= 0).any():
             return                       # a server without work this step: keep the current shares
         self.last_measured = allv

@@ -160,3 +160,57 @@ def test_blocking_report_names_the_waits_that_kept_the_stream_idle():
     assert rep == [{"step": 7, "wait": "qkv", "index": 1, "ms": 3.5}, {"step": 7, "wait": "dout", "index": 0, "ms": 1.2}]
     assert CadRuntime.blocking_report(waits, threshold_ms=10.0) == []
     assert CadRuntime.blocking_report([], threshold_ms=0.0) == []
+
+
+def test_end_of_step_feedback_with_stand_in_events(monkeypatch):
+    """The bookkeeping of one step's attention / wait events (CUDA events on a GPU, stand-ins with a fake clock
+    here): measured and idle time reach the planner's shares through the group collective, the wait report keeps
+    the waits above its threshold, and the per-step lists are emptied."""
+    import torch.distributed as dist
+
+    class Ev:
+        clock = [0.0]
+        step = [1.0]
+
+        def __init__(self, enable_timing=False):
+            self.t = None
+
+        def record(self, stream=None):
+            Ev.clock[0] += Ev.step[0]
+            self.t = Ev.clock[0]
+
+        def elapsed_time(self, other):
+            return other.t - self.t
+
+    monkeypatch.setattr(torch.cuda, "Event", Ev)
+    created = not dist.is_initialized()
+    if created:
+        dist.init_process_group("gloo", init_method="tcp://127.0.0.1:29733", rank=0, world_size=1)
+    try:
+        rt = _runtime(0, 1, 1024)
+        rt.use_cost_model = rt.speed_feedback = True
+        rt.group, rt.speed, rt.predicted_ms, rt._predicted_ms = dist.group.WORLD, None, 80.0, 0.0
+        rt._attn_events, rt._wait_events, rt.blocking_events, rt._steps_seen = [], [], [], 0
+        rt.wait_report_ms = 10.0
+        for layer in range(3):
+            Ev.step[0] = 0.5 if layer != 1 else 25.0            # the wait of layer 1 keeps the stream idle for 25 ms
+            with rt._timed_wait("qkv"):
+                pass
+            Ev.step[0] = 30.0
+            with rt._timed_attention(0.25):
+                pass
+        rt.end_of_step_feedback()
+        assert rt.blocking_events == [{"step": 1, "wait": "qkv", "index": 1, "ms": 25.0}]
+        assert rt._attn_events == [] and rt._wait_events == [] and rt._predicted_ms == 0.0
+        assert rt.plan_stats["attention_ms_per_server"] == [90.0] and rt.plan_stats["idle_ms_per_server"] == [26.0]
+        assert rt.plan_stats["speed"] == [1.0] and rt._pending_speed == [1.0]
+        rt.wait_report_ms = None                                  # off: events are still consumed, nothing is recorded
+        with rt._timed_wait("out"):
+            pass
+        with rt._timed_attention(1.0):
+            pass
+        rt.end_of_step_feedback()
+        assert len(rt.blocking_events) == 1 and rt._steps_seen == 2
+    finally:
+        if created:
+            dist.destroy_process_group()
