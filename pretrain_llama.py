@@ -59,6 +59,10 @@ def parse_args(argv=None):
     ap.add_argument("--quit-if-maybe-oom", action="store_true",
                     help="estimate the per-GPU memory of the configuration first and refuse to start if it does not fit")
     ap.add_argument("--torch-profile-step", type=int, default=-1, help="write a torch.profiler chrome trace of this step")
+    ap.add_argument("--trace-calls-step", type=int,
+                    default=0 if os.environ.get("EXPERIMENT_PYTHON_DEBUG_TRACE_CALLS", "0") == "1" else -1,
+                    help="log every Python call of this package during this step to <output-dir>/calls.rank{r}.log "
+                         "(which rank is stuck where; heavy)")
     ap.add_argument("--span-documents", action="store_true",
                     help="lay the documents of a global batch out over the ranks by sequential fill, so a document "
                          "may be longer than one rank's tokens (--max-total-tokens bounds its length); needs --cad, no pipeline")
@@ -221,8 +225,19 @@ def main(argv=None) -> int:
         if world > 1:
             dist.barrier()
         t0 = time.perf_counter()
-        with nvtx_range(f"sample_{it}"), ProfilerCtx(a.output_dir, rank, enabled=(it == a.torch_profile_step)):
-            loss = trainer.train_step(hb)
+        calls = None
+        if it == a.trace_calls_step:
+            from distca_b200.utils.profiler import TraceFunctions
+            os.makedirs(a.output_dir or ".", exist_ok=True)
+            calls = TraceFunctions(out=open(os.path.join(a.output_dir or ".", f"calls.rank{rank}.log"), "w"))
+            calls.__enter__()
+        try:
+            with nvtx_range(f"sample_{it}"), ProfilerCtx(a.output_dir, rank, enabled=(it == a.torch_profile_step)):
+                loss = trainer.train_step(hb)
+        finally:
+            if calls is not None:
+                calls.__exit__(None, None, None)
+                calls.out.close()
         guards.check(it, loss, float(trainer.opt.last_grad_norm) if trainer.opt.last_grad_norm is not None else None)
         if torch.cuda.is_available():
             torch.cuda.synchronize()

@@ -122,3 +122,15 @@ def test_bench_named_configs_are_the_contract_layouts():
     m = get_model_config("codellama-34b")
     assert (m.num_layers, m.hidden, m.heads_q, m.heads_kv, m.ffn, m.vocab) == (48, 8192, 64, 8, 22016, 32000)
     assert c["34b_256k"]["recompute"] == "full" and c["34b_256k"]["seq_len"] == 262144
+
+
+def test_cli_call_trace_and_profile_of_one_step(tmp_path):
+    """--trace-calls-step writes the Python calls of this package during that step (which rank is where),
+    --torch-profile-step a chrome trace of that step."""
+    out = str(tmp_path / "run")
+    _run(["--model", "tiny", "--num-layers", "1", "--num-tokens", "256", "--sample-name", "loguniform64", "--output-dir", out,
+          "--max-sample-id", "2", "--trace-calls-step", "1", "--torch-profile-step", "1"], str(tmp_path))
+    calls = open(os.path.join(out, "calls.rank0.log")).read()
+    assert "-> train_step (trainer.py:" in calls and "<- train_step" in calls and "forward_backward" in calls
+    trace = json.load(open(os.path.join(out, "trace.rank0.json")))
+    assert trace["traceEvents"]
