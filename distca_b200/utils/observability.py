@@ -58,6 +58,47 @@ def nvtx_range(name: str):
             torch.cuda.nvtx.range_pop()
 
 
+class MemoryHistory:
+    """Allocation history of the PyTorch caching allocator: ``start()`` begins recording, an out-of-memory error
+    writes ``oom.rank{r}.pickle`` (the state at the failing allocation), ``dump()`` writes
+    ``memory.rank{r}.pickle`` (e.g. after the first steps); both open in PyTorch's memory visualiser. The
+    reference does this under ``--record-memory-history`` (distca/runtime/megatron/model_patch.py:204-215) and
+    plots a timeline in its tests (tests/test_megatron_e2e.py:395-424). The peer arenas are ``cudaMalloc``'d by
+    this repository's library and do not appear there: ``MemoryLog`` reports them through NVML. Without a GPU
+    every method does nothing and returns ``None``."""
+
+    def __init__(self, out_dir: str | None, rank: int, max_entries: int = 100000):
+        self.dir, self.rank, self.max_entries = out_dir, rank, max_entries
+        self.active = False
+
+    def _path(self, stem: str) -> str:
+        os.makedirs(self.dir, exist_ok=True)
+        return os.path.join(self.dir, f"{stem}.rank{self.rank}.pickle")
+
+    def start(self):
+        if self.dir is None or not torch.cuda.is_available():
+            return None
+        torch.cuda.memory._record_memory_history(max_entries=self.max_entries)
+        self.active = True
+
+        def on_oom(device, alloc, device_alloc, device_free):
+            torch.cuda.memory._dump_snapshot(self._path("oom"))
+        torch._C._cuda_attach_out_of_memory_observer(on_oom)
+        return self
+
+    def dump(self):
+        if not self.active:
+            return None
+        path = self._path("memory")
+        torch.cuda.memory._dump_snapshot(path)
+        return path
+
+    def stop(self) -> None:
+        if self.active:
+            torch.cuda.memory._record_memory_history(enabled=None)
+            self.active = False
+
+
 class MemoryLog:
     def __init__(self, out_dir: str | None, rank: int, enabled: bool = True):
         self.enabled = enabled and out_dir is not None

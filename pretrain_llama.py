@@ -59,6 +59,9 @@ def parse_args(argv=None):
     ap.add_argument("--quit-if-maybe-oom", action="store_true",
                     help="estimate the per-GPU memory of the configuration first and refuse to start if it does not fit")
     ap.add_argument("--torch-profile-step", type=int, default=-1, help="write a torch.profiler chrome trace of this step")
+    ap.add_argument("--record-memory-history", action="store_true",
+                    help="record the caching allocator's history: memory.rank{r}.pickle after the second step and "
+                         "oom.rank{r}.pickle when an allocation fails (PyTorch memory visualiser format)")
     ap.add_argument("--trace-calls-step", type=int,
                     default=0 if os.environ.get("EXPERIMENT_PYTHON_DEBUG_TRACE_CALLS", "0") == "1" else -1,
                     help="log every Python call of this package during this step to <output-dir>/calls.rank{r}.log "
@@ -169,6 +172,10 @@ def main(argv=None) -> int:
     art = RunArtifacts(a.output_dir, rank)
     art.write_config({"args": vars(a), "model": cfg.__dict__, "parallel": par.__dict__, "world": world})
     mem = MemoryLog(a.output_dir, rank, enabled=a.log_memory)
+    mem_hist = None
+    if a.record_memory_history:
+        from distca_b200.utils.observability import MemoryHistory
+        mem_hist = MemoryHistory(a.output_dir or ".", rank).start()
     from distca_b200.utils.observability import MetricsSink
     sink = MetricsSink(a.enable_wandb, rank, a.wandb_project, a.wandb_run_name, vars(a), a.output_dir)
     # with CAD the phase timers are always on: they give the exposed dispatch time and the attention time per
@@ -260,6 +267,8 @@ def main(argv=None) -> int:
         art.step(rec)
         sink.log(rec)
         mem.log(f"step_{it}")
+        if mem_hist is not None and it == start_it + 1:
+            log.info("allocator history written to %s", mem_hist.dump())
         log.info("step %d loss %.4f %.1f ms %.0f tok/s%s", it, loss, ms, rec["tokens_per_s"],
                  f" imbalance {rec['attn_imbalance']:.3f}" if rec.get("attn_imbalance") else "")
         if a.val_every_n_steps and (it + 1) % a.val_every_n_steps == 0 and not percp:
