@@ -681,6 +681,7 @@ class LlamaModel:
         self._nano_stream_objs = None
         self.store_sync_group = None       # gloo-capable group over which the keep_attn placement is agreed
         self.attn_store_placement = None   # "device" | "host" to override the automatic choice
+        self.check_finite = False          # debug: test every layer's output / input gradient (one sync per layer pass)
 
     def _attn_store(self, tokens: int, host_copies: int = 1):
         """Store of the per-layer core-attention outputs for ``recompute="keep_attn"`` (created at the
@@ -813,6 +814,12 @@ class LlamaModel:
         return loss_sum, dx
 
     # ---- whole-stage passes ----
+    def _finite(self, t, what: str, index: int) -> None:
+        """Debug aid (``check_finite``): name the first layer pass that produced a NaN / Inf, like the reference's
+        NaN hooks (playground/utils/nan_detector.py:165-444)."""
+        if self.check_finite and t is not None and not bool(torch.isfinite(t).all()):
+            raise FloatingPointError(f"non-finite values in the {what} of layer {index}")
+
     def forward_backward(self, batch: Batch, core_attn, *, x_in: torch.Tensor | None = None,
                          dy_in: torch.Tensor | None = None):
         """One micro-batch through this stage. Returns (loss or None, dx_to_previous_stage or None)."""
@@ -827,6 +834,7 @@ class LlamaModel:
             with timers.layer("fwd", layer.index):
                 x, ctx = layer.forward(x, batch.pos, self.rope_table, core_attn, keep,
                                        attn_store=store if store is not None and store.has(layer.index) else None)
+            self._finite(x, "forward output", layer.index)
             ctxs.append(ctx)
         with timers.phase("lm_head"):
             loss, dx = self.head_loss_and_grad(x, batch.labels, batch.num_valid_global)
@@ -849,6 +857,7 @@ class LlamaModel:
             inputs[i] = None
             with timers.layer("bwd", layer.index):
                 dx = layer.backward(ctx, dx, batch.pos, self.rope_table, core_attn)
+            self._finite(dx, "input gradient", layer.index)
             del ctx
             if self.grad_ready_hook is not None:
                 self.grad_ready_hook(list(layer.names.values()))

@@ -182,6 +182,7 @@ class Trainer:
         for layer in self.model.layers:
             layer.fuse_rope = bool(train_cfg.extra.get("fuse_qkv_rope", True))
         self.model.nano_streams = bool(train_cfg.extra.get("nano_streams", True))
+        self.model.check_finite = bool(train_cfg.extra.get("check_finite", False))
         if self.groups is not None and self.device.type == "cuda":
             self.model.store_sync_group = self.groups.world_group
         self.core_attn = LocalCoreAttention(model_cfg, par.tp)

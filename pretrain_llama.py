@@ -59,6 +59,9 @@ def parse_args(argv=None):
     ap.add_argument("--quit-if-maybe-oom", action="store_true",
                     help="estimate the per-GPU memory of the configuration first and refuse to start if it does not fit")
     ap.add_argument("--torch-profile-step", type=int, default=-1, help="write a torch.profiler chrome trace of this step")
+    ap.add_argument("--check-finite", action="store_true",
+                    help="debug: test every layer's output and input gradient for NaN / Inf and name the first one "
+                         "(one device synchronisation per layer pass; non-pipelined, one nano-batch)")
     ap.add_argument("--record-memory-history", action="store_true",
                     help="record the caching allocator's history: memory.rank{r}.pickle after the second step and "
                          "oom.rank{r}.pickle when an allocation fails (PyTorch memory visualiser format)")
@@ -157,6 +160,7 @@ def main(argv=None) -> int:
     tc.extra["dp_transport"] = a.dp_transport
     if a.wait_report_ms is not None:
         tc.extra["wait_report_ms"] = a.wait_report_ms
+    tc.extra["check_finite"] = a.check_finite
     if a.baseline_mode == "percp" and a.pp_size > 1:
         raise SystemExit("--baseline-mode percp has no pipeline stages: use --pp-size 1")
     tc.extra["nano_batches"] = 2 if (a.pingpong and cad and a.pp_size == 1 and world > 1 and not a.span_documents) else 1   # ping-pong nano-batches (non-pipelined trainer)

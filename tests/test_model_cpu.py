@@ -95,3 +95,23 @@ def test_rotary_table_grows_for_documents_longer_than_max_position():
         ca.set_batch(AttnPlan(AttnTasks.from_doc_lens(doc_lens), "cpu", need_backward=False))
         losses.append(m.forward_loss(batch, ca).item())
     assert abs(losses[0] - losses[1]) < 1e-9
+
+
+def test_finite_check_names_the_layer_that_produced_the_first_nan():
+    cfg = ModelConfig(name="t", num_layers=3, hidden=64, heads_q=4, heads_kv=2, head_dim=16, ffn=96, vocab=128,
+                      max_position=512)
+    doc_lens = [40, 24]
+    model = LlamaModel(cfg, "cpu", dtype=torch.float64, recompute="full", lm_head_chunk=50)
+    batch = _batch(cfg, doc_lens)
+    ca = LocalCoreAttention(cfg)
+    ca.set_batch(AttnPlan(AttnTasks.from_doc_lens(doc_lens), "cpu", need_backward=False))
+    model.check_finite = True
+    model.store.zero_grad()
+    loss, _ = model.forward_backward(batch, ca)            # clean weights: nothing raised
+    assert torch.isfinite(loss)
+    model.store.p["decoder.layers.1.mlp.linear_fc2.weight"][0, 0] = float("nan")
+    with pytest.raises(FloatingPointError, match="forward output of layer 1"):
+        model.forward_backward(batch, ca)
+    model.check_finite = False
+    loss, _ = model.forward_backward(batch, ca)            # without the check the NaN only shows in the loss
+    assert not torch.isfinite(loss)
