@@ -59,6 +59,9 @@ def parse_args(argv=None):
     ap.add_argument("--quit-if-maybe-oom", action="store_true",
                     help="estimate the per-GPU memory of the configuration first and refuse to start if it does not fit")
     ap.add_argument("--torch-profile-step", type=int, default=-1, help="write a torch.profiler chrome trace of this step")
+    ap.add_argument("--bind-cpus", action="store_true",
+                    help="bind every rank to its own contiguous slice of the host's CPUs and write the per-rank "
+                         "environment record (<output-dir>/envs/)")
     ap.add_argument("--check-finite", action="store_true",
                     help="debug: test every layer's output and input gradient for NaN / Inf and name the first one "
                          "(one device synchronisation per layer pass; non-pipelined, one nano-batch)")
@@ -173,6 +176,11 @@ def main(argv=None) -> int:
                                              microbatches_in_flight=min(a.num_microbatch, a.pp_size) if a.pp_size > 1 else 1),
                           cap)
     log = get_logger(rank=rank, out_dir=a.output_dir)
+    if a.bind_cpus:
+        from distca_b200.utils import affinity
+        affinity.bind(local, int(os.environ.get("LOCAL_WORLD_SIZE", a.num_gpus_per_node or world)), logger=log)
+        if a.output_dir:
+            affinity.dump_environment(a.output_dir, rank, local)
     art = RunArtifacts(a.output_dir, rank)
     art.write_config({"args": vars(a), "model": cfg.__dict__, "parallel": par.__dict__, "world": world})
     mem = MemoryLog(a.output_dir, rank, enabled=a.log_memory)

@@ -254,3 +254,28 @@ def test_step_model_reproduces_the_measured_one_gpu_step_and_orders_the_tensor_p
     res = search_layouts("llama3-8b", 8, 32768, "mixture", iterations=1)
     for r in res["layouts"]:
         assert ("step_ms_percp" in r) == (r["pp"] == 1 and r["dp"] > 1)
+
+
+def test_cpu_affinity_slices_are_disjoint_and_the_environment_record_is_written(tmp_path):
+    import os
+    from distca_b200.utils import affinity
+    cpus = list(range(4, 68))                                      # 64 allowed CPUs, not starting at 0
+    slices = [affinity.plan_affinity(r, 8, cpus) for r in range(8)]
+    assert all(len(s) == 8 for s in slices) and sorted(c for s in slices for c in s) == cpus
+    assert slices[3] == list(range(28, 36)) and affinity.format_cpus(slices[3]) == "28-35"
+    assert affinity.plan_affinity(1, 8, cpus, per_proc=4) == [12, 13, 14, 15]
+    assert affinity.plan_affinity(5, 8, [0, 1, 2]) == [2]          # fewer CPUs than ranks: shared, not an error
+    assert affinity.format_cpus([0, 1, 2, 3, 8, 9, 11]) == "0-3,8-9,11"
+    before = affinity.allowed_cpus()
+    try:
+        mine = affinity.bind(0, 1)
+        assert mine == before and affinity.allowed_cpus() == before
+        if len(before) >= 2:
+            half = affinity.bind(1, 2)
+            assert affinity.allowed_cpus() == half and len(half) == len(before) // 2
+    finally:
+        if hasattr(os, "sched_setaffinity"):
+            os.sched_setaffinity(0, before)
+    path = affinity.dump_environment(str(tmp_path), rank=3, local_rank=1)
+    text = open(path).read()
+    assert path.endswith(".r3.lr1.env") and "PATH=" in text and "# cpus: " in text
