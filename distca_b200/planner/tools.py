@@ -182,7 +182,8 @@ def predict_step_ms(cfg, tm, packs: list[list[int]], tokens: int, tp: int, pp: i
 
 def search_layouts(model: str, gpus: int, tokens: int, dist: str, iterations: int = 10, tolerance: float = 0.02,
                    seed: int = 0, microbatches: int | None = None, seqs_per_step: int | None = None,
-                   recompute: str = "keep_attn", tp_transport: str = "gather") -> dict:
+                   recompute: str = "keep_attn", tp_transport: str = "gather", comm_buffer_gb: float = 4.0,
+                   capacity_gb: float = 180.0) -> dict:
     """Predicted milliseconds per training step of a fixed global batch of ``seqs_per_step`` packed sequences
     (default: one per GPU) under every (tp, pp, dp) layout of ``gpus`` GPUs, with local attention, with core-attention
     disaggregation and (layouts without pipeline stages) with the per-document CP baseline."""
@@ -209,12 +210,24 @@ def search_layouts(model: str, gpus: int, tokens: int, dist: str, iterations: in
                    "step_ms_local_attention": round(res["local"], 1), "step_ms_cad": round(res["cad"], 1)}
             if "percp" in res:
                 row["step_ms_percp"] = round(res["percp"], 1)
+            # per-GPU memory of the layout with disaggregation (tokens of one micro-batch per data-parallel rank)
+            from ..models.config import ParallelConfig
+            from ..utils.guards import estimate_memory_gb
+            tok_mb = (seqs // dp) * tokens // (M if pp > 1 else 1)
+            est = estimate_memory_gb(cfg, ParallelConfig(tp=tp, pp=pp, dp=dp), tok_mb, recompute=recompute,
+                                     cad=dp * pp > 1, comm_buffer_gb=comm_buffer_gb,
+                                     microbatches_in_flight=min(M, pp) if pp > 1 else 1)
+            row["memory_gb"] = round(est["total"], 1)
+            row["fits"] = bool(est["total"] <= capacity_gb * 0.97)
             rows.append(row)
-    rows.sort(key=lambda r: min(r["step_ms_local_attention"], r["step_ms_cad"]))
+    # layouts that fit first, fastest first
+    rows.sort(key=lambda r: (not r["fits"], min(r["step_ms_local_attention"], r["step_ms_cad"])))
     return {"model": cfg.name, "gpus": gpus, "tokens_per_sequence": tokens, "sequences_per_step": seqs, "dist": dist,
-            "recompute": recompute, "tp_transport": tp_transport, "layouts": rows,
-            "note": "predicted from the attention table, the per-token linear time and the link bandwidth of the B200 "
-                    "time model, calibrated on one measured step; memory limits are not checked here"}
+            "recompute": recompute, "tp_transport": tp_transport, "capacity_gb": capacity_gb, "layouts": rows,
+            "note": "time: predicted from the attention table, the per-token linear time and the link bandwidth of the "
+                    "B200 time model, calibrated on one measured step; memory: the pre-flight estimate of "
+                    "utils/guards.py (keep_attn is counted like full recompute: kept attention outputs go to "
+                    "whatever HBM is left, then to host memory)"}
 
 
 def main() -> None:
@@ -229,13 +242,16 @@ def main() -> None:
     ap.add_argument("--seqs-per-step", type=int, default=None, help="layouts: packed sequences per step (default: one per GPU)")
     ap.add_argument("--microbatches", type=int, default=None, help="layouts: micro-batches per step of the pipelined layouts")
     ap.add_argument("--recompute", default="keep_attn", choices=["none", "full", "keep_attn"])
+    ap.add_argument("--comm-buffer-gb", type=float, default=4.0)
+    ap.add_argument("--capacity-gb", type=float, default=180.0, help="layouts: HBM per GPU")
     ap.add_argument("--tp-transport", default="gather", choices=["gather", "tile", "nccl"],
                     help="layouts: how a tensor-parallel all-gather reaches its GEMM (gather = --tp-transport p2p)")
     a = ap.parse_args()
     if a.tool == "layouts":
         print(json.dumps(search_layouts(a.model, a.world, a.tokens, a.dist, a.iterations, a.tolerance,
                                         microbatches=a.microbatches, seqs_per_step=a.seqs_per_step,
-                                        recompute=a.recompute, tp_transport=a.tp_transport)))
+                                        recompute=a.recompute, tp_transport=a.tp_transport,
+                                        comm_buffer_gb=a.comm_buffer_gb, capacity_gb=a.capacity_gb)))
         return
     f = {"buffer": recommend_buffer_gb, "compare": compare_policies}[a.tool]
     print(json.dumps(f(a.model, a.world, a.tokens, a.dist, a.iterations, a.tolerance)))
