@@ -189,6 +189,8 @@ def run_named_config(a) -> None:
     tc = TrainConfig(cad=not (a.no_cad or percp), recompute=recompute, comm_buffer_gb=a.comm_buffer_gb)
     tc.extra.update(tolerance=a.tolerance, attention_policy=a.attention_policy, fuse_qkv_rope=not a.no_fuse_qkv_rope,
                     baseline_mode=a.baseline_mode)
+    if pp > 1 and tc.cad:
+        tc.extra["nano_batches"] = a.nano_batches     # ping-pong nano-batches inside the pipeline stages
     if pp > 1:
         from distca_b200.parallel.pipeline import PipelineTrainer
         trainer = PipelineTrainer(cfg, par, tc, num_microbatch=M, seed=0)
@@ -268,6 +270,7 @@ def run_named_config(a) -> None:
             "config": {"model": cfg.name, "layers": cfg.num_layers, "global_batch": seqs_per_step, "seq_len": seq_len,
                        "parallelism": f"tp{tp}-" + (f"cp{dp}-percp" if percp else f"pp{pp}-dp{dp}" + ("-cad" if cad_rt is not None else "")),
                        "microbatches": M if pp > 1 else 1, "recompute": recompute,
+                       "nano_batches": int(tc.extra.get("nano_batches", 1)),
                        "grad_dtype": str(trainer.model.store.grad.dtype).replace("torch.", ""),
                        "tp_transport": "p2p" if (tp > 1 and getattr(trainer.model.tp, "use_p2p", False)) else ("nccl" if tp > 1 else None),
                        "dp_transport": "p2p" if getattr(trainer, "p2p", None) is not None else ("nccl" if dp > 1 else None),

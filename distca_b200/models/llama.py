@@ -1027,6 +1027,73 @@ class LlamaModel:
             dx = None
         return loss, dx
 
+    def stage_forward_nano(self, batches, cas, x_ins):
+        """:meth:`stage_forward` for the nano-batches of one micro-batch, interleaved layer by layer (ping-pong
+        inside a pipeline stage; the reference runs its ping-pong layers under the pipeline schedule the same
+        way, distca/runtime/megatron/ping_pong/transformer_block.py:234-344 under
+        forward_backward_func.py:117-519). ``batches[k]`` / ``x_ins[k]`` are ``None`` for a nano-batch this rank
+        owns no tokens of (it still serves attention for it). Returns ``(x_outs, saved)``."""
+        n = len(batches)
+        xs = [None] * n
+        for k, b in enumerate(batches):
+            if b is not None:
+                xs[k] = self.embed(b.ids) if self.first_stage else x_ins[k]
+        poss = [b.pos if b is not None else None for b in batches]
+        stores = [_ListStore() for _ in range(n)] if self.recompute == "keep_attn" else None
+        inputs, ctxs = [], []
+        for layer in self.layers:
+            keep = self.recompute == "none"
+            inputs.append(xs)
+            with timers.layer("fwd", layer.index):
+                outs = layer.forward_nano(xs, poss, self.rope_table, cas, keep, stores=stores)
+            xs = [o[0] for o in outs]
+            ctxs.append([o[1] for o in outs] if keep else None)
+        return xs, (inputs, ctxs, xs if self.last_stage else None, stores)
+
+    def stage_backward_nano(self, batches, cas, saved, dys, grads_final: bool = False):
+        """:meth:`stage_backward` for the nano-batches of one micro-batch (see :meth:`stage_forward_nano`).
+        Returns ``(summed loss or None, [dx per nano-batch] or None on the first stage)``."""
+        inputs, ctxs, x_outs, stores = saved
+        n = len(batches)
+        poss = [b.pos if b is not None else None for b in batches]
+        loss = None
+        if self.last_stage:
+            dxs = [None] * n
+            for k, b in enumerate(batches):
+                if b is None:
+                    continue
+                with timers.phase("lm_head"):
+                    l, dxs[k] = self.head_loss_and_grad(x_outs[k], b.labels, b.num_valid_global)
+                loss = l if loss is None else loss + l
+        else:
+            dxs = list(dys)
+        del x_outs
+        for i in reversed(range(len(self.layers))):
+            layer = self.layers[i]
+            cs = ctxs[i]
+            ctxs[i] = None
+            if cs is None:
+                kept = None
+                if stores is not None:
+                    kept = [stores[k].load(layer.index) if inputs[i][k] is not None else None for k in range(n)]
+                with timers.layer("recompute", layer.index):
+                    outs = layer.forward_nano(inputs[i], poss, self.rope_table, cas, True, saved=kept, need_output=False)
+                cs = [o[1] for o in outs]
+                del kept, outs
+            inputs[i] = None
+            with timers.layer("bwd", layer.index):
+                dxs = layer.backward_nano(cs, dxs, poss, self.rope_table, cas)
+            del cs
+            if grads_final and self.grad_ready_hook is not None:
+                self.grad_ready_hook(list(layer.names.values()))
+        if self.first_stage:
+            for k, b in enumerate(batches):
+                if b is not None:
+                    with timers.phase("embed_bwd"):
+                        self.embed_bwd(b.ids, dxs[k])
+            dxs = None
+        return loss, dxs
+
     def forward_loss(self, batch: Batch, core_attn) -> torch.Tensor:
         """Evaluation pass (no gradients)."""
         x = self.embed(batch.ids)

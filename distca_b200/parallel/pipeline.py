@@ -103,6 +103,22 @@ class PipelineTrainer:
             from .cad_cpu import GlooCadRuntime
             self.cad = GlooCadRuntime(model_cfg, self.groups.attn_group, self.groups.attn_ranks, par.tp,
                                       tolerance=float(train_cfg.extra.get("tolerance", 0.1)), dtype=self.model.dtype)
+        # ping-pong inside the stages: every micro-batch is cut into two nano-batches, each with its own
+        # core-attention runtime (own arena, signals and per-slot plans), interleaved layer by layer
+        self.nano = int(train_cfg.extra.get("nano_batches", 1))
+        assert self.nano in (1, 2)
+        assert self.nano == 1 or self.cad is not None, "nano-batches in pipeline stages need core-attention disaggregation"
+        self.cads = [self.cad] if self.cad is not None else []
+        if self.nano == 2:
+            if on_gpu:
+                from .cad import CadRuntime
+                self.cads.append(CadRuntime(model_cfg, par, train_cfg, self.groups, self.device,
+                                            tolerance=float(train_cfg.extra.get("tolerance", 0.1))))
+            else:
+                from .cad_cpu import GlooCadRuntime
+                self.cads.append(GlooCadRuntime(model_cfg, self.groups.attn_group, self.groups.attn_ranks, par.tp,
+                                                tolerance=float(train_cfg.extra.get("tolerance", 0.1)),
+                                                dtype=self.model.dtype))
         repl = tuple(n for n, _ in self.model.store.shapes if n.endswith("norm_weight") or n.endswith("layernorm.weight"))
         self.opt = ShardedAdam(self.model.store, train_cfg, dp_group=self.groups.dp_group if par.dp > 1 else None,
                                norm_group=self.groups.world_group, replicated_names=repl if par.tp > 1 else (),
@@ -162,31 +178,53 @@ class PipelineTrainer:
             self._plan_pool = ThreadPoolExecutor(max_workers=1, thread_name_prefix="cad-planner")
         futs = {}
 
-        def work(docs, cad=self.cad):
+        def work(docs, cad):
             plan = cad.make_plan(docs)
             return plan, (cad.make_tables(plan) if plan.fits else None)
+        per_nano = self._nano_docs(all_mb_docs)
         for f, b in slot_schedule(len(all_mb_docs), self.par.pp):
             for which, slot in (("fwd", f), ("bwd", b)):
                 if slot is not None:
-                    futs[(which, slot)] = self._plan_pool.submit(work, self._slot_docs(all_mb_docs, which, slot))
+                    for k, cad in enumerate(self.cads):
+                        futs[(which, slot, k)] = self._plan_pool.submit(work, self._slot_docs(per_nano[k], which, slot), cad)
         return futs
+
+    def _arenas_ready(self) -> bool:
+        """Sizing an arena is a collective: plans are only made on the planning thread once every runtime has one."""
+        return all(getattr(c, "arena", None) is not None for c in self.cads)
+
+    def _nano_docs(self, all_mb_docs):
+        """``[nano-batch][micro-batch][dp rank]`` document lists: with two nano-batches every rank's documents of
+        a micro-batch are cut at the document boundary nearest to half its tokens (the rule of
+        ``runtime.trainer.nano_cut``, applied by every rank to every rank's list, so all agree)."""
+        if self.nano == 1:
+            return [all_mb_docs]
+        from ..runtime.trainer import nano_cut
+        halves = ([], [])
+        for mb in all_mb_docs:
+            cuts = [nano_cut(d) for d in mb]
+            halves[0].append([list(d[:c]) for d, c in zip(mb, cuts)])
+            halves[1].append([list(d[c:]) for d, c in zip(mb, cuts)])
+        return list(halves)
 
     def prefetch_plan(self, hb_next) -> None:
         """Plan every slot of the NEXT step on the planning thread while the current step runs."""
-        if self.cad is None or not hasattr(self.cad, "make_tables") or getattr(self.cad, "arena", None) is None:
+        if self.cad is None or not hasattr(self.cad, "make_tables") or not self._arenas_ready():
             return
         _, all_mb_docs = self._microbatch_docs(hb_next)
         self._plans_ahead = (all_mb_docs, self._submit_plans(all_mb_docs))
 
     def _set_attention(self, all_mb_docs, plans, which, slot, mb):
         if self.cad is not None:
-            docs = self._slot_docs(all_mb_docs, which, slot)
-            fut = plans.get((which, slot)) if plans else None
-            if fut is not None:
-                plan, tables = fut.result()
-                self.cad.plan_step(docs, plan=plan, tables=tables)
-            else:
-                self.cad.plan_step(docs)
+            per_nano = self._nano_docs(all_mb_docs)
+            for k, cad in enumerate(self.cads):
+                docs = self._slot_docs(per_nano[k], which, slot)
+                fut = plans.get((which, slot, k)) if plans else None
+                if fut is not None:
+                    plan, tables = fut.result()
+                    cad.plan_step(docs, plan=plan, tables=tables)
+                else:
+                    cad.plan_step(docs)
             return self.cad
         if 0 <= mb < self.M:
             self.local_attn.set_batch(AttnPlan(AttnTasks.from_doc_lens(all_mb_docs[mb][self.dp_rank]), self.device))
@@ -212,11 +250,16 @@ class PipelineTrainer:
             self.model.tp.ensure_fused(T // self.par.tp)
         Tl = T // self.par.tp
         H = self.model_cfg.hidden
+        nano_batches = self._split_nano_batches(all_mb_docs, batches) if self.nano == 2 else None
+        if self.nano == 2:
+            for cad in self.cads:
+                if hasattr(cad, "capacity_hint"):
+                    cad.capacity_hint = max(cad.capacity_hint, T)     # a nano-batch can be the whole micro-batch
         plans = None
         if self.cad is not None and hasattr(self.cad, "make_tables"):
             if self._plans_ahead is not None and self._plans_ahead[0] == all_mb_docs:
                 plans = self._plans_ahead[1]
-            elif getattr(self.cad, "arena", None) is not None:
+            elif self._arenas_ready():
                 plans = self._submit_plans(all_mb_docs)
             self._plans_ahead = None
         saved = {}
@@ -235,15 +278,22 @@ class PipelineTrainer:
                     ca = self._set_attention(all_mb_docs, plans, "fwd", f, f_mb)
                     if plans is None and self.cad is not None and hasattr(self.cad, "make_tables") and tick == 0:
                         plans = self._submit_plans(all_mb_docs)      # the arena exists now: plan the rest ahead
-                        plans.pop(("fwd", f), None)
+                        for k in range(len(self.cads)):
+                            plans.pop(("fwd", f, k), None)
                     x_out = None
-                    if 0 <= f_mb < M:
+                    if 0 <= f_mb < M and self.nano == 2:
+                        real += 1
+                        nb, rows = nano_batches[f_mb]
+                        x_outs, saved[f_mb] = self.model.stage_forward_nano(nb, self.cads, self._split_rows(x_in, rows))
+                        x_out = self._join_rows(x_outs) if not self.last else None
+                    elif 0 <= f_mb < M:
                         real += 1
                         x_out, saved[f_mb] = self.model.stage_forward(batches[f_mb], ca, x_in,
                                                                       keep_last=self.last and self.cad is None)
                     elif self.cad is not None:
                         for _ in range(n_layers):
-                            self.cad.dummy_forward()
+                            for cad in self.cads:
+                                cad.dummy_forward()
                     nf = f_mb + 1          # what this stage runs in its next forward slot
                     more = f + 1 < M + pp - 1
                     pend_x = self._start_exchange(
@@ -257,7 +307,15 @@ class PipelineTrainer:
                     pend_dy = None
                     ca = self._set_attention(all_mb_docs, plans, "bwd", b, b_mb)
                     dx = None
-                    if 0 <= b_mb < M:
+                    if 0 <= b_mb < M and self.nano == 2:
+                        real += 1
+                        nb, rows = nano_batches[b_mb]
+                        loss, dxs = self.model.stage_backward_nano(nb, self.cads, saved.pop(b_mb),
+                                                                   self._split_rows(dy_in, rows), grads_final=(b_mb == M - 1))
+                        dx = self._join_rows(dxs) if dxs is not None else None
+                        if loss is not None:
+                            loss_sum += loss
+                    elif 0 <= b_mb < M:
                         real += 1
                         loss, dx = self.model.stage_backward(batches[b_mb], ca, saved.pop(b_mb), dy_in,
                                                              grads_final=(b_mb == M - 1))
@@ -265,13 +323,16 @@ class PipelineTrainer:
                             loss_sum += loss
                     elif self.cad is not None:
                         for li in range(n_layers):
-                            if self.model.recompute == "keep_attn":
-                                # the recompute half only re-dispatches Q/K/V (nothing to send from here), no attention runs
-                                self.cad.no_tokens_dispatch()
-                                self.cad.restore_no_tokens(li)
-                            else:
-                                self.cad.dummy_forward()    # the recompute half of a backward slot
-                            self.cad.dummy_backward()
+                            # same order of calls per runtime as a stage that runs a real micro-batch
+                            for cad in self.cads:
+                                if self.model.recompute == "keep_attn":
+                                    # the recompute half only re-dispatches Q/K/V (nothing to send from here), no attention runs
+                                    cad.no_tokens_dispatch()
+                                    cad.restore_no_tokens(li)
+                                else:
+                                    cad.dummy_forward()    # the recompute half of a backward slot
+                            for cad in self.cads:
+                                cad.dummy_backward()
                     nb = b_mb + 1
                     more = b + 1 < M + pp - 1
                     pend_dy = self._start_exchange(
@@ -291,10 +352,42 @@ class PipelineTrainer:
         loss_sum /= self.par.tp
         self.step_idx += 1
         value = float(loss_sum.item())
-        if self.cad is not None and hasattr(self.cad, "end_of_step_feedback"):
-            self.cad.end_of_step_feedback()
+        for cad in self.cads:
+            if hasattr(cad, "end_of_step_feedback"):
+                cad.end_of_step_feedback()
         self.check_device_status()      # raises when a kernel of this step reported a failed wait / bounds check
         return value
+
+    def _split_nano_batches(self, all_mb_docs, batches):
+        """Per micro-batch: ([Batch or None per nano-batch], [sequence-parallel rows per nano-batch]) of THIS rank."""
+        from ..runtime.trainer import nano_cut
+        out = []
+        for mb, b in zip(all_mb_docs, batches):
+            docs = mb[self.dp_rank]
+            t0 = sum(docs[:nano_cut(docs)])
+            T = int(b.ids.numel())
+            assert t0 % self.par.tp == 0 and (T - t0) % self.par.tp == 0, "nano-batch rows must divide by the tensor-parallel size"
+            parts = []
+            for lo, hi in ((0, t0), (t0, T)):
+                parts.append(Batch(b.ids[lo:hi], b.labels[lo:hi], b.pos[lo:hi], b.num_valid_global) if hi > lo else None)
+            out.append((parts, [t0 // self.par.tp, (T - t0) // self.par.tp]))
+        return out
+
+    @staticmethod
+    def _split_rows(x, rows):
+        """The stage input (or gradient) of a micro-batch as one tensor per nano-batch (``None`` where empty)."""
+        if x is None:
+            return [None] * len(rows)
+        out, lo = [], 0
+        for r in rows:
+            out.append(x[lo:lo + r] if r else None)
+            lo += r
+        return out
+
+    @staticmethod
+    def _join_rows(parts):
+        parts = [t for t in parts if t is not None]
+        return parts[0] if len(parts) == 1 else torch.cat(parts, dim=0)
 
     def _microbatch_docs(self, hb):
         """(tokens per micro-batch, documents [micro-batch][dp rank]) of a host batch."""
@@ -329,6 +422,8 @@ class PipelineTrainer:
         loss_sum = torch.zeros((), dtype=torch.float32, device=self.device)
         x_in = None
         keep_policy, self.model.recompute = self.model.recompute, "full"     # nothing is kept for a backward
+        keep_nano, keep_cads = self.nano, self.cads
+        self.nano, self.cads = 1, self.cads[:1]                              # evaluation runs whole micro-batches
         try:
             for tick in range(M + pp - 1):
                 f_mb = tick - p
@@ -350,6 +445,7 @@ class PipelineTrainer:
                     (Tl, H) if (not self.first and 0 <= nf < M) else None, self.prev))
         finally:
             self.model.recompute = keep_policy
+            self.nano, self.cads = keep_nano, keep_cads
         dist.all_reduce(loss_sum, group=self.groups.world_group)
         loss_sum /= self.par.tp
         return float(loss_sum.item())
@@ -364,9 +460,9 @@ class PipelineTrainer:
             self._plan_pool.shutdown(wait=True)
             self._plan_pool = None
         self.guard.close()
-        if self.cad is not None:
-            self.cad.close()
-            self.cad = None
+        for cad in self.cads:
+            cad.close()
+        self.cads, self.cad = [], None
         if self.par.tp > 1 and getattr(self.model.tp, "fused", None) is not None:
             self.model.tp.fused.close()
             self.model.tp.fused = None

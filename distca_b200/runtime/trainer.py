@@ -91,19 +91,24 @@ def make_span_batch(rng: np.random.Generator, world: int, tokens_per_rank: int, 
     return SpanHostBatch(docs, toks)
 
 
+def nano_cut(docs: list[int]) -> int:
+    """Number of leading documents of ``docs`` that form the first nano-batch: the document boundary closest
+    to half the tokens (0 or ``len(docs)`` when one document holds more than half of them)."""
+    total, best, run, k = sum(docs), None, 0, 0
+    for i in range(len(docs) + 1):
+        d = abs(2 * run - total)
+        if best is None or d < best:
+            best, k = d, i
+        if i < len(docs):
+            run += docs[i]
+    return k
+
+
 def split_nano(hb: HostBatch) -> list[HostBatch]:
     """Cut one rank's batch into two nano-batches at the document boundary closest to half its
     tokens (every rank applies the same rule to every rank's document list, so all agree on who owns
     what in each nano-batch). A nano-batch may be empty (one document filling the whole sequence)."""
-    def cut(docs):
-        total, best, run, k = sum(docs), None, 0, 0
-        for i in range(len(docs) + 1):
-            d = abs(2 * run - total)
-            if best is None or d < best:
-                best, k = d, i
-            if i < len(docs):
-                run += docs[i]
-        return k
+    cut = nano_cut
     per_rank = [(d[:cut(d)], d[cut(d):]) for d in hb.all_doc_lens]
     k = cut(hb.doc_lens)
     t0 = sum(hb.doc_lens[:k])

@@ -166,7 +166,8 @@ def main(argv=None) -> int:
     tc.extra["check_finite"] = a.check_finite
     if a.baseline_mode == "percp" and a.pp_size > 1:
         raise SystemExit("--baseline-mode percp has no pipeline stages: use --pp-size 1")
-    tc.extra["nano_batches"] = 2 if (a.pingpong and cad and a.pp_size == 1 and world > 1 and not a.span_documents) else 1   # ping-pong nano-batches (non-pipelined trainer)
+    # ping-pong nano-batches: in the non-pipelined trainer and inside pipeline stages alike
+    tc.extra["nano_batches"] = 2 if (a.pingpong and cad and dp * a.pp_size > 1 and not a.span_documents) else 1
     if a.quit_if_maybe_oom:
         import torch as _t
         from distca_b200.utils.guards import estimate_memory_gb, quit_if_maybe_oom

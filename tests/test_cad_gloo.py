@@ -48,6 +48,8 @@ def _worker(rank, world, port, pp, q, cad_recompute="full", nano=1, tp=1):
             out[mode] = (loss, tr.model.store.grad.clone())
             if mode == "cad":
                 stats = dict(tr.cad.plan_stats)
+                stats["runtimes"] = len(getattr(tr, "cads", None) or getattr(tr, "core_attns", [tr.cad]))
+                stats["schedule"] = getattr(tr, "last_schedule", None)
         dl = abs(out["local"][0] - out["cad"][0])
         g0, g1 = out["local"][1], out["cad"][1]
         dg = (g0 - g1).abs().max().item()
@@ -105,3 +107,16 @@ def test_cad_tp2_pp2_world4():
     """The 4-D layout in small: tensor-parallel pairs, two pipeline stages, one attention group per
     tensor-parallel index over the pipeline stages."""
     _run(4, 2, "full", tp=2)
+
+
+@pytest.mark.parametrize("recompute", ["full", "keep_attn"])
+def test_cad_ping_pong_inside_pipeline_stages_world2(recompute):
+    """Two nano-batches per micro-batch interleaved layer by layer inside the 1F1B schedule: every micro-batch is
+    cut at a document boundary, each half has its own runtime and its own plan per slot, idle slots serve both."""
+    res = _run(2, 2, recompute, nano=2)
+    assert all(r[4]["runtimes"] == 2 and r[4]["schedule"]["ticks"] == 4 for r in res)
+
+
+def test_cad_ping_pong_tp2_pp2_world4():
+    res = _run(4, 2, "keep_attn", nano=2, tp=2)
+    assert all(r[4]["runtimes"] == 2 for r in res)

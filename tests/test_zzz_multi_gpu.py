@@ -105,3 +105,11 @@ def test_documents_spanning_ranks_train_like_the_per_document_cp_baseline():
     per-document CP baseline on the same global batches."""
     res = _run(2, 29551, ["--tokens", "4096", "--steps", "3"], check="span")
     assert res["ok"] and res["longest_document"] > res["tokens_per_rank"] // 2, res
+
+
+@pytest.mark.skipif(_ngpu() < 2, reason="needs 2 GPUs")
+def test_cad_pp2_pingpong_inside_pipeline_stages():
+    """Two nano-batches per micro-batch, each with its own runtime (arena, signals, per-slot plans), interleaved
+    layer by layer inside the 1F1B schedule; idle slots serve both."""
+    res = _run(2, 29552, ["--tokens", "4096", "--pp", "2", "--microbatches", "3", "--nano", "2", "--recompute", "keep_attn"])
+    assert res["ok"], res
