@@ -89,8 +89,9 @@ def _args():
 
 
 def reference_arm(a) -> None:
-    """The reference trains through Megatron-LM + TransformerEngine + its NVSHMEM library; none of
-    them is present offline, so its public entry point cannot start."""
+    """The reference trains through Megatron-LM + TransformerEngine (+ omegaconf); none of them is present
+    offline, so its public entry point cannot start. Its own communication layer does build and run here: that
+    arm is ``python -m distca_b200.utils.fa2a_bench --impl reference``."""
     why = None
     ref = os.path.join(os.path.dirname(os.path.abspath(__file__)), "baseline", "_ref")
     if not os.path.isdir(os.path.join(ref, "distca")):
@@ -103,8 +104,9 @@ def reference_arm(a) -> None:
             except Exception:
                 missing.append(mod)
         if missing:
-            why = ("reference installs (pure Python) but its training path imports " + ", ".join(missing) +
-                   " and loads libas_comm.so (NVSHMEM build); none are available offline")
+            why = ("the reference's training entry point imports " + ", ".join(missing) + ", absent offline (its package "
+                   "installs and its NVSHMEM library builds for sm_100a: the communication arm runs, "
+                   "python -m distca_b200.utils.fa2a_bench --impl reference)")
         else:
             why = "reference dependencies present but its launcher is not wired on this box"
     if int(os.environ.get("RANK", "0")) == 0:
