@@ -130,7 +130,17 @@ class CadRuntime:
         self.planner = Planner(PlannerConfig(world=W, tokens_per_rank=T, tolerance=self.tolerance,
                                              q_row_bytes=self.q_bytes, kv_row_bytes=self.kv_bytes,
                                              max_q_rows=self.max_q, max_kv_rows=self.max_kv,
-                                             cost_model=default_cost_model(self.hq) if self.use_cost_model else None))
+                                             cost_model=self._cost_model() if self.use_cost_model else None))
+
+    def _cost_model(self) -> dict:
+        """The balancer's cost model: fitted to a measured sweep when ``extra["cost_model_file"]`` names one
+        (``kernel_bench --kernel attn_sweep`` output of this machine), else the built-in B200 constants."""
+        path = self.tcfg.extra.get("cost_model_file")
+        if path:
+            from ..planner import cost_model_from_sweep
+            cm = cost_model_from_sweep(path, heads_q=self.hq)
+            return {k: cm[k] for k in ("tile", "ms_per_tile_pair", "ms_per_q_tile", "ms_per_task")}
+        return default_cost_model(self.hq)
 
     # ------------------------------------------------------------------------------------------
     def make_plan(self, docs_per_rank: list[list[int]]):

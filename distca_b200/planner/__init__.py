@@ -157,6 +157,74 @@ def default_cost_model(heads_q: int = 32, kind: str = "b200") -> dict:
     return {"tile": 128, "ms_per_tile_pair": 9.68e-4 * s, "ms_per_q_tile": 3.5e-3 * s, "ms_per_task": 0.0}
 
 
+def _sweep_rows(source) -> list[dict]:
+    """Rows of ``python -m distca_b200.utils.kernel_bench --kernel attn_sweep`` (one JSON object per line; a path, an
+    open file or an iterable of lines / dicts). Lines that are not sweep rows are skipped."""
+    import json
+    if isinstance(source, (str, bytes)) or hasattr(source, "__fspath__"):
+        with open(source) as f:
+            lines = list(f)
+    else:
+        lines = list(source)
+    rows = []
+    for ln in lines:
+        if isinstance(ln, dict):
+            d = ln
+        else:
+            ln = ln.strip()
+            if not ln.startswith("{"):
+                continue
+            try:
+                d = json.loads(ln)
+            except ValueError:
+                continue
+        if d.get("kernel") == "attn_sweep" and "fwd_ms" in d and "bwd_ms" in d:
+            rows.append(d)
+    return rows
+
+
+def cost_model_from_sweep(source, heads_q: int | None = None, tile: int = 128) -> dict:
+    """Fit the balancer's cost model to a measured sweep: relative least squares of
+    ``fwd_ms + bwd_ms = a * tile_pairs + b * query_tiles`` over the sweep's workloads (every workload counts alike,
+    whatever its size). ``heads_q``: query heads on the rank the model is for (default: the sweep's own); the
+    constants scale with it. This is how the constants of :func:`default_cost_model` are re-derived for another
+    GPU, clock or kernel version (the reference loads its profile tables the same way,
+    distca/timemodule/compute.py:23-72)."""
+    import numpy as np
+    rows = _sweep_rows(source)
+    if len(rows) < 2:
+        raise ValueError("a cost-model fit needs at least two attn_sweep rows")
+    X, y = [], []
+    for d in rows:
+        n = int(d["seqlen"]) // tile
+        docs = int(d.get("docs", 1))
+        X.append([float(d.get("tile_pairs", docs * n * (n + 1) // 2)), float(d.get("query_tiles", docs * n))])
+        y.append(float(d["fwd_ms"]) + float(d["bwd_ms"]))
+    X, y = np.asarray(X), np.asarray(y)
+    w = 1.0 / y
+    coef, *_ = np.linalg.lstsq(X * w[:, None], y * w, rcond=None)
+    a, b = float(coef[0]), float(max(coef[1], 0.0))
+    if a <= 0.0:
+        raise ValueError(f"fit gave a non-positive cost per tile pair ({a}); the sweep does not span enough lengths")
+    pred = X @ np.array([a, b])
+    sweep_heads = int(rows[0].get("heads", [32])[0]) if isinstance(rows[0].get("heads"), (list, tuple)) else 32
+    s = (heads_q or sweep_heads) / float(sweep_heads)
+    return {"tile": tile, "ms_per_tile_pair": a * s, "ms_per_q_tile": b * s, "ms_per_task": 0.0,
+            "max_rel_err": float(np.max(np.abs(pred - y) / y)), "workloads": len(rows)}
+
+
+def time_model_from_sweep(source, base: str = "b200"):
+    """The simulator's time model with its attention table replaced by the sweep's whole-document forward times
+    (rows with one document), everything else as in :func:`default_time_model`."""
+    rows = sorted((r for r in _sweep_rows(source) if int(r.get("docs", 1)) == 1), key=lambda r: int(r["seqlen"]))
+    if len(rows) < 2:
+        raise ValueError("a time-model table needs at least two single-document attn_sweep rows")
+    tm = default_time_model(base)
+    tm.attn_len = [float(r["seqlen"]) for r in rows]
+    tm.attn_ms = [float(r["fwd_ms"]) for r in rows]
+    return tm
+
+
 def default_time_model(kind: str = "b200"):
     """Attention/linear cost tables. ``b200``: measured with this repository's kernels on one B200
     (whole causal document, 32 query / 8 KV heads of 128, forward); ``h100``: the reference's

@@ -183,12 +183,12 @@ def predict_step_ms(cfg, tm, packs: list[list[int]], tokens: int, tp: int, pp: i
 def search_layouts(model: str, gpus: int, tokens: int, dist: str, iterations: int = 10, tolerance: float = 0.02,
                    seed: int = 0, microbatches: int | None = None, seqs_per_step: int | None = None,
                    recompute: str = "keep_attn", tp_transport: str = "gather", comm_buffer_gb: float = 4.0,
-                   capacity_gb: float = 180.0) -> dict:
+                   capacity_gb: float = 180.0, time_model=None) -> dict:
     """Predicted milliseconds per training step of a fixed global batch of ``seqs_per_step`` packed sequences
     (default: one per GPU) under every (tp, pp, dp) layout of ``gpus`` GPUs, with local attention, with core-attention
     disaggregation and (layouts without pipeline stages) with the per-document CP baseline."""
     cfg = get_model_config(model)
-    tm = default_time_model("b200")
+    tm = time_model if time_model is not None else default_time_model("b200")
     seqs = seqs_per_step or gpus
     src = SyntheticBatches(tokens, seqs, dist, seed)
     batches = [src.next_doc_lens() for _ in range(iterations)]
@@ -246,12 +246,18 @@ def main() -> None:
     ap.add_argument("--capacity-gb", type=float, default=180.0, help="layouts: HBM per GPU")
     ap.add_argument("--tp-transport", default="gather", choices=["gather", "tile", "nccl"],
                     help="layouts: how a tensor-parallel all-gather reaches its GEMM (gather = --tp-transport p2p)")
+    ap.add_argument("--sweep-file", default=None,
+                    help="layouts: `kernel_bench --kernel attn_sweep` output of the target machine for the attention table")
     a = ap.parse_args()
     if a.tool == "layouts":
+        tm = None
+        if a.sweep_file:
+            from . import time_model_from_sweep
+            tm = time_model_from_sweep(a.sweep_file)
         print(json.dumps(search_layouts(a.model, a.world, a.tokens, a.dist, a.iterations, a.tolerance,
                                         microbatches=a.microbatches, seqs_per_step=a.seqs_per_step,
                                         recompute=a.recompute, tp_transport=a.tp_transport,
-                                        comm_buffer_gb=a.comm_buffer_gb, capacity_gb=a.capacity_gb)))
+                                        comm_buffer_gb=a.comm_buffer_gb, capacity_gb=a.capacity_gb, time_model=tm)))
         return
     f = {"buffer": recommend_buffer_gb, "compare": compare_policies}[a.tool]
     print(json.dumps(f(a.model, a.world, a.tokens, a.dist, a.iterations, a.tolerance)))

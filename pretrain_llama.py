@@ -59,6 +59,9 @@ def parse_args(argv=None):
     ap.add_argument("--quit-if-maybe-oom", action="store_true",
                     help="estimate the per-GPU memory of the configuration first and refuse to start if it does not fit")
     ap.add_argument("--torch-profile-step", type=int, default=-1, help="write a torch.profiler chrome trace of this step")
+    ap.add_argument("--cost-model-file", default=None,
+                    help="output of `python -m distca_b200.utils.kernel_bench --kernel attn_sweep` on this machine: the "
+                         "planner's attention cost model is fitted to it instead of the built-in B200 constants")
     ap.add_argument("--bind-cpus", action="store_true",
                     help="bind every rank to its own contiguous slice of the host's CPUs and write the per-rank "
                          "environment record (<output-dir>/envs/)")
@@ -164,6 +167,8 @@ def main(argv=None) -> int:
     if a.wait_report_ms is not None:
         tc.extra["wait_report_ms"] = a.wait_report_ms
     tc.extra["check_finite"] = a.check_finite
+    if a.cost_model_file:
+        tc.extra["cost_model_file"] = a.cost_model_file
     if a.baseline_mode == "percp" and a.pp_size > 1:
         raise SystemExit("--baseline-mode percp has no pipeline stages: use --pp-size 1")
     # ping-pong nano-batches: in the non-pipelined trainer and inside pipeline stages alike

@@ -221,3 +221,37 @@ def test_balancer_with_cost_model_and_server_speeds():
         (ha, hb), (ta, tb) = it["head"], it["tail"]
         q[it["doc"]] = q.get(it["doc"], 0) + hb - ha + tb - ta
     assert sorted(q.values()) == sorted(L for d in docs for L in d)
+
+
+def test_cost_and_time_models_fitted_from_a_measured_sweep(tmp_path):
+    """``kernel_bench --kernel attn_sweep`` output -> the balancer's cost model (relative least squares) and the
+    simulator's attention table; other lines of the log are skipped."""
+    import json
+    from distca_b200.planner import cost_model_from_sweep, default_cost_model, time_model_from_sweep
+    a, b = 1.0e-3, 2.0e-3
+    rows = []
+    for L, docs in [(2048, 16), (4096, 8), (8192, 1), (16384, 1), (32768, 1)]:
+        n = L // 128
+        pairs, qt = docs * n * (n + 1) // 2, docs * n
+        total = a * pairs + b * qt
+        rows.append({"kernel": "attn_sweep", "seqlen": L, "docs": docs, "heads": [32, 8], "fwd_ms": 0.25 * total,
+                     "bwd_ms": 0.75 * total, "tile_pairs": pairs, "query_tiles": qt})
+    p = tmp_path / "sweep.jsonl"
+    p.write_text("warming up\n" + "\n".join(json.dumps(r) for r in rows)
+                 + '\n{"kernel": "attn_sweep_fit", "ms_per_tile_pair": 1.0}\nnot json {\n')
+    cm = cost_model_from_sweep(str(p))
+    assert abs(cm["ms_per_tile_pair"] - a) < 1e-9 and abs(cm["ms_per_q_tile"] - b) < 1e-9 and cm["max_rel_err"] < 1e-9
+    assert cm["workloads"] == 5 and cm["tile"] == 128
+    half = cost_model_from_sweep(rows, heads_q=16)                   # a rank with half the query heads
+    assert abs(half["ms_per_tile_pair"] - a / 2) < 1e-9
+    # the three measured workloads of one B200: the fit stays within a few per cent of every one of them
+    meas = [{"kernel": "attn_sweep", "seqlen": 8192, "docs": 1, "fwd_ms": 0.5347, "bwd_ms": 1.7322},
+            {"kernel": "attn_sweep", "seqlen": 32768, "docs": 1, "fwd_ms": 7.2401, "bwd_ms": 25.5859},
+            {"kernel": "attn_sweep", "seqlen": 2048, "docs": 16, "fwd_ms": 0.6636, "bwd_ms": 2.0348}]
+    fit = cost_model_from_sweep(meas)
+    assert fit["max_rel_err"] < 0.03 and 0.5 < fit["ms_per_tile_pair"] / default_cost_model(32)["ms_per_tile_pair"] < 1.5
+    tm = time_model_from_sweep(rows)
+    assert list(tm.attn_len) == [8192.0, 16384.0, 32768.0] and abs(tm.attn_ms_for(8192, 8192) - rows[2]["fwd_ms"]) < 1e-9
+    import pytest
+    with pytest.raises(ValueError):
+        cost_model_from_sweep(rows[:1])
