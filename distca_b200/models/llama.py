@@ -424,7 +424,7 @@ class LlamaLayer:
         return y, LayerCtx(x, rstd1, n1f, ca_ctx, attn_out, h, rstd2, n2f, pre, act)
 
     def forward_nano(self, xs, poss, rope_table, cas, keep: bool, stores=None, saved=None, need_output: bool = True,
-                     streams=None):
+                     streams=None, pre=None, next_layer=None):
         """Forward of this layer for several nano-batches, ping-pong order: every nano-batch runs
         pre-CA (which dispatches its Q/K/V), then every attention server call is issued, and only then
         does each nano-batch collect its attention output and run post-CA, so one nano-batch's
@@ -434,15 +434,22 @@ class LlamaLayer:
         included) is queued on ``streams[k]``, so while one nano-batch waits for its servers the GPU runs the
         other's kernels (the reference's compute / communication stream pair with ``TickSync``,
         distca/runtime/megatron/ping_pong/transformer_block.py:122-129, 234-344, ops/stream_sync_fn.py:80-136).
+        ``next_layer`` (tick fusion): as soon as nano-batch ``k`` has its output, the NEXT layer's pre-CA runs for
+        it (its Q/K/V leave for the servers before the other nano-batch's post-CA of this layer starts), and the
+        results come back as a second return value to be passed to that layer as ``pre``; the reference fuses
+        post-CA of layer l-1 with pre-CA of layer l into one tick the same way
+        (distca/runtime/megatron/ping_pong/tick_ops.py:338-354).
         Reference: distca/runtime/megatron/ping_pong/transformer_layer.py:260-417."""
         n = len(xs)
-        pre = [None] * n
-        for k in range(n):
-            with _on(streams, k):
-                if xs[k] is None:
-                    cas[k].no_tokens_dispatch()
-                else:
-                    pre[k] = self.pre_ca(xs[k], poss[k], rope_table, cas[k])
+        if pre is None:
+            pre = [None] * n
+            for k in range(n):
+                with _on(streams, k):
+                    if xs[k] is None:
+                        cas[k].no_tokens_dispatch()
+                    else:
+                        pre[k] = self.pre_ca(xs[k], poss[k], rope_table, cas[k])
+        pre_next = [None] * n if next_layer is not None else None
         saving = stores is not None and not keep     # keep_attn: O and its statistics are stored per layer
         if saved is None:
             for k in range(n):
@@ -457,6 +464,8 @@ class LlamaLayer:
                 if xs[k] is None:
                     if saved is not None:
                         cas[k].restore_no_tokens(self.index)
+                    if next_layer is not None:
+                        cas[k].no_tokens_dispatch()          # the next layer's (empty) dispatch of this nano-batch
                     outs.append((None, None))
                     continue
                 qkv, n1f, rstd1 = pre[k]
@@ -466,6 +475,10 @@ class LlamaLayer:
                     stores[k].save(self.index, cas[k].pack_saved(attn_out, ca_ctx), clone=False)
                 y, h, rstd2, n2f, prea, act = self.post_ca(xs[k], attn_out, keep, need_output)
                 outs.append((y, LayerCtx(xs[k], rstd1, n1f, ca_ctx, attn_out, h, rstd2, n2f, prea, act) if keep else None))
+                if next_layer is not None:
+                    pre_next[k] = next_layer.pre_ca(y, poss[k], rope_table, cas[k])
+        if next_layer is not None:
+            return outs, pre_next
         return outs
 
     def backward_nano(self, cs, dys, poss, rope_table, cas, streams=None):
@@ -682,6 +695,7 @@ class LlamaModel:
         self.store_sync_group = None       # gloo-capable group over which the keep_attn placement is agreed
         self.attn_store_placement = None   # "device" | "host" to override the automatic choice
         self.check_finite = False          # debug: test every layer's output / input gradient (one sync per layer pass)
+        self.fuse_ticks = False            # ping-pong: pre-CA of layer l+1 right after post-CA of layer l per nano-batch
 
     def _attn_store(self, tokens: int, host_copies: int = 1):
         """Store of the per-layer core-attention outputs for ``recompute="keep_attn"`` (created at the
@@ -890,12 +904,16 @@ class LlamaModel:
         if self.recompute == "keep_attn":
             stores = self._attn_stores([x.shape[0] if x is not None else 0 for x in xs])
         ctxs, inputs = [], []
+        pre = None
         for i, layer in enumerate(self.layers):
             keep = self.recompute == "none" or i == nl - 1
             inputs.append(xs)
             use = stores if stores is not None and stores[0].has(layer.index) else None
+            nxt = self.layers[i + 1] if (self.fuse_ticks and i + 1 < nl) else None
             with timers.layer("fwd", layer.index):
-                outs = layer.forward_nano(xs, poss, self.rope_table, cas, keep, stores=use, streams=streams)
+                outs = layer.forward_nano(xs, poss, self.rope_table, cas, keep, stores=use, streams=streams,
+                                          pre=pre, next_layer=nxt)
+            outs, pre = outs if nxt is not None else (outs, None)
             xs = [o[0] for o in outs]
             ctxs.append([o[1] for o in outs] if keep else None)
         losses = []
@@ -1041,11 +1059,14 @@ class LlamaModel:
         poss = [b.pos if b is not None else None for b in batches]
         stores = [_ListStore() for _ in range(n)] if self.recompute == "keep_attn" else None
         inputs, ctxs = [], []
-        for layer in self.layers:
+        pre, nl = None, len(self.layers)
+        for i, layer in enumerate(self.layers):
             keep = self.recompute == "none"
             inputs.append(xs)
+            nxt = self.layers[i + 1] if (self.fuse_ticks and i + 1 < nl) else None
             with timers.layer("fwd", layer.index):
-                outs = layer.forward_nano(xs, poss, self.rope_table, cas, keep, stores=stores)
+                outs = layer.forward_nano(xs, poss, self.rope_table, cas, keep, stores=stores, pre=pre, next_layer=nxt)
+            outs, pre = outs if nxt is not None else (outs, None)
             xs = [o[0] for o in outs]
             ctxs.append([o[1] for o in outs] if keep else None)
         return xs, (inputs, ctxs, xs if self.last_stage else None, stores)

@@ -93,6 +93,7 @@ class PipelineTrainer:
                                 pad_params_to=par.dp, param_buffers=buffers)
         for layer in self.model.layers:
             layer.fuse_rope = bool(train_cfg.extra.get("fuse_qkv_rope", True))
+        self.model.fuse_ticks = bool(train_cfg.extra.get("fuse_ticks", False))
         self.local_attn = LocalCoreAttention(model_cfg, par.tp)
         self.cad = None
         if train_cfg.cad and par.dp * par.pp > 1 and on_gpu:

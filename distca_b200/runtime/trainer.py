@@ -188,6 +188,7 @@ class Trainer:
             layer.fuse_rope = bool(train_cfg.extra.get("fuse_qkv_rope", True))
         self.model.nano_streams = bool(train_cfg.extra.get("nano_streams", True))
         self.model.check_finite = bool(train_cfg.extra.get("check_finite", False))
+        self.model.fuse_ticks = bool(train_cfg.extra.get("fuse_ticks", False))
         if self.groups is not None and self.device.type == "cuda":
             self.model.store_sync_group = self.groups.world_group
         self.core_attn = LocalCoreAttention(model_cfg, par.tp)

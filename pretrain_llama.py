@@ -117,6 +117,9 @@ def parse_args(argv=None):
                     help="two nano-batches per rank and step, interleaved layer by layer (the reference's ping-pong "
                          "schedule); off by default, like bench.py: on one stream it measured the same speed")
     ap.add_argument("--no-pingpong", dest="pingpong", action="store_false")
+    ap.add_argument("--fuse-ticks", action="store_true",
+                    help="with --pingpong: per nano-batch, run the next layer's pre-attention half (and its Q/K/V "
+                         "dispatch) right after this layer's post-attention half, as the reference's fused ticks do")
     ap.add_argument("--save", default=None, help="checkpoint directory (Megatron layout)")
     ap.add_argument("--load", default=None)
     ap.add_argument("--save-interval", type=int, default=0)
@@ -167,6 +170,7 @@ def main(argv=None) -> int:
     if a.wait_report_ms is not None:
         tc.extra["wait_report_ms"] = a.wait_report_ms
     tc.extra["check_finite"] = a.check_finite
+    tc.extra["fuse_ticks"] = a.fuse_ticks
     if a.cost_model_file:
         tc.extra["cost_model_file"] = a.cost_model_file
     if a.baseline_mode == "percp" and a.pp_size > 1:

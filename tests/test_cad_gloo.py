@@ -22,7 +22,7 @@ def _free_port():
     return p
 
 
-def _worker(rank, world, port, pp, q, cad_recompute="full", nano=1, tp=1):
+def _worker(rank, world, port, pp, q, cad_recompute="full", nano=1, tp=1, extra=None):
     try:
         os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port), RANK=str(rank), WORLD_SIZE=str(world),
                           LOCAL_RANK=str(rank))
@@ -37,6 +37,7 @@ def _worker(rank, world, port, pp, q, cad_recompute="full", nano=1, tp=1):
                              lm_head_chunk=2048, lr=0.0)
             if mode == "cad":
                 tc.extra["nano_batches"] = nano
+                tc.extra.update(extra or {})
             if pp > 1:
                 from distca_b200.parallel.pipeline import PipelineTrainer
                 tr = PipelineTrainer(cfg, par, tc, num_microbatch=2, device="cpu", seed=0)
@@ -62,11 +63,11 @@ def _worker(rank, world, port, pp, q, cad_recompute="full", nano=1, tp=1):
         q.put((rank, False, repr(e), traceback.format_exc(), None))
 
 
-def _run(world, pp, cad_recompute="full", nano=1, tp=1):
+def _run(world, pp, cad_recompute="full", nano=1, tp=1, extra=None):
     ctx = mp.get_context("spawn")
     q = ctx.Queue()
     port = _free_port()
-    procs = [ctx.Process(target=_worker, args=(r, world, port, pp, q, cad_recompute, nano, tp)) for r in range(world)]
+    procs = [ctx.Process(target=_worker, args=(r, world, port, pp, q, cad_recompute, nano, tp, extra)) for r in range(world)]
     for p in procs:
         p.start()
     results = [q.get(timeout=600) for _ in range(world)]
@@ -120,3 +121,10 @@ def test_cad_ping_pong_inside_pipeline_stages_world2(recompute):
 def test_cad_ping_pong_tp2_pp2_world4():
     res = _run(4, 2, "keep_attn", nano=2, tp=2)
     assert all(r[4]["runtimes"] == 2 for r in res)
+
+
+@pytest.mark.parametrize("pp,recompute", [(1, "full"), (1, "keep_attn"), (2, "keep_attn")])
+def test_cad_ping_pong_with_fused_ticks_world2(pp, recompute):
+    """Tick fusion: per nano-batch the next layer's pre-CA (and its Q/K/V dispatch) follows this layer's post-CA
+    directly, before the other nano-batch's post-CA; the result must not change."""
+    _run(2, pp, recompute, nano=2, extra={"fuse_ticks": True})
