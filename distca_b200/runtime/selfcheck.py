@@ -50,6 +50,7 @@ def check_cad(a) -> int:
                          grad_dtype="fp32" if a.pp > 1 else "bf16")
         if mode == "cad":
             tc.extra["nano_batches"] = a.nano
+            tc.extra["fuse_ticks"] = a.fuse_ticks
         if a.pp > 1:
             from ..parallel.pipeline import PipelineTrainer
             tr = PipelineTrainer(cfg, par, tc, num_microbatch=a.microbatches, seed=1)
@@ -252,6 +253,7 @@ def main() -> None:
     ap.add_argument("--pp", type=int, default=1)
     ap.add_argument("--microbatches", type=int, default=2)
     ap.add_argument("--nano", type=int, default=1, choices=[1, 2], help="ping-pong nano-batches in the CAD run")
+    ap.add_argument("--fuse-ticks", action="store_true", help="with --nano 2: the next layer's pre-attention half per nano-batch right after this layer's post-attention half")
     ap.add_argument("--recompute", default="full", choices=["full", "keep_attn"],
                     help="activation policy of the CAD run (the local run always recomputes fully)")
     a = ap.parse_args()
