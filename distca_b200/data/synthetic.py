@@ -2,8 +2,8 @@
 
 Document-length samplers: log-uniform in a range, the long/short mixture used for 128K-256K
 context runs (80 % log-uniform in [128, 8192], 20 % log-uniform in [32768, L_max]), and
-bundled histograms in the style of the reference's ``wlbllm`` / ``prolong`` samples
-(distca/simulator/optimizers/samples.py:152-250). ``pack_documents`` fills fixed-size token
+the ``wlbllm`` / ``prolong`` length distributions of the reference's data sets, reproduced from their quantiles
+and shaped by the same up-sample / filter / elongate options (distca/simulator/optimizers/samples.py:152-250). ``pack_documents`` fills fixed-size token
 buffers, carrying the overflow of a document into the next pack and rounding lengths up to a
 multiple of 16 (samples.py:253-305).
 
@@ -30,20 +30,53 @@ def sample_mixture(rng: np.random.Generator, n: int, max_len: int, short=(128, 8
     return np.where(is_long, l, s)
 
 
-def sample_histogram(rng: np.random.Generator, n: int, kind: str, max_len: int) -> np.ndarray:
-    """Heavy-tailed stand-ins for the reference's dataset histograms (the JSON samples themselves
-    are data files of the reference and are not redistributed): ``wlbllm`` is dominated by short
-    documents with a thin tail to the context limit, ``prolong`` has most mass above 8K."""
-    if kind == "wlbllm":
-        x = rng.lognormal(mean=6.8, sigma=1.4, size=n)
-    elif kind == "prolong":
-        x = rng.lognormal(mean=9.6, sigma=1.1, size=n)
-    else:
+# Quantiles of the document-length samples the reference ships for its two data sets (summary statistics of
+# distca/simulator/data/dist_wlbllm.json, 99 519 documents, mean 3 962 tokens, and dist_prolong.json, 77 932
+# documents, mean 3 052; the samples themselves are the reference's data and are not redistributed). Both are
+# dominated by documents of a few thousand tokens with a thin tail: 0.9 % (wlbllm) / 0.2 % (prolong) of the
+# documents reach 32K tokens, and they hold 17 % / 5 % of all tokens.
+_Q = (0.0, 0.01, 0.05, 0.10, 0.25, 0.50, 0.75, 0.90, 0.95, 0.99, 0.995, 0.999, 1.0)
+_LENGTH_QUANTILES = {
+    "wlbllm": (1, 63, 324, 646, 1606, 3227, 4832, 5784, 6110, 26058, 69097, 119793, 124913),
+    "prolong": (575, 678, 801, 919, 1237, 1913, 3467, 6051, 8378, 16269, 21357, 47397, 340149),
+}
+
+
+def _cdf(kind: str, length: float) -> float:
+    """Fraction of the ``kind`` documents shorter than ``length`` (log-linear between the quantile knots)."""
+    q, v = np.asarray(_Q), np.log(np.asarray(_LENGTH_QUANTILES[kind], dtype=np.float64))
+    return float(np.interp(math.log(max(length, 1.0)), v, q, left=0.0, right=1.0))
+
+
+def sample_histogram(rng: np.random.Generator, n: int, kind: str, max_len: int, *, up_sample_factor: int = 1,
+                     filter_threshold: int = 10000, filter_ratio: float = 1.0, elongate_factor: int = 1,
+                     change_long_doc_ratio: float = 0.0) -> np.ndarray:
+    """``n`` document lengths from the ``wlbllm`` / ``prolong`` length distributions (inverse-CDF sampling through
+    the quantile table above), shaped the way the reference shapes its samples
+    (distca/simulator/optimizers/samples.py:152-250): documents shorter than ``filter_threshold`` are kept with
+    probability ``filter_ratio``, longer ones count ``up_sample_factor`` times; ``wlbllm`` lengths are multiplied by
+    ``elongate_factor``; in ``prolong`` a long document becomes a full context of ``65536 * elongate_factor`` tokens
+    with probability ``change_long_doc_ratio``. Lengths are clipped to ``[16, max_len]``."""
+    if kind not in _LENGTH_QUANTILES:
         raise ValueError(kind)
+    q, logv = np.asarray(_Q), np.log(np.asarray(_LENGTH_QUANTILES[kind], dtype=np.float64))
+    f_thr = _cdf(kind, filter_threshold)                       # probability mass of the short documents
+    w_short, w_long = f_thr * max(filter_ratio, 0.0), (1.0 - f_thr) * max(int(up_sample_factor), 1)
+    p_long = w_long / (w_short + w_long) if (w_short + w_long) > 0 else 0.0
+    is_long = rng.random(n) < p_long
+    u = rng.random(n)
+    u = np.where(is_long, f_thr + u * (1.0 - f_thr), u * f_thr)
+    x = np.exp(np.interp(u, q, logv))
+    if kind == "wlbllm":
+        x = x * max(int(elongate_factor), 1)
+    else:
+        full = is_long & (rng.random(n) < change_long_doc_ratio)
+        x = np.where(full, 65536.0 * max(int(elongate_factor), 1), x)
     return np.clip(x, 16, max_len).astype(np.int64)
 
 
-def sample_doc_lens(rng: np.random.Generator, n: int, name: str, max_len: int) -> np.ndarray:
+def sample_doc_lens(rng: np.random.Generator, n: int, name: str, max_len: int, **shape) -> np.ndarray:
+    """``shape``: the modifiers of :func:`sample_histogram` (only the data-set distributions have them)."""
     if name == "loguniform":
         return sample_loguniform(rng, n, 128, max_len)
     if name == "loguniform64":
@@ -51,7 +84,7 @@ def sample_doc_lens(rng: np.random.Generator, n: int, name: str, max_len: int) -
     if name == "mixture":
         return sample_mixture(rng, n, max_len)
     if name in ("wlbllm", "prolong"):
-        return sample_histogram(rng, n, name, max_len)
+        return sample_histogram(rng, n, name, max_len, **shape)
     if name == "full":
         return np.full(n, max_len, dtype=np.int64)
     raise ValueError(f"unknown document-length distribution {name!r}")
@@ -82,17 +115,20 @@ class SyntheticBatches:
     """Endless stream of global batches: ``num_seqs`` packs of ``tokens_per_seq`` tokens each."""
 
     def __init__(self, tokens_per_seq: int, num_seqs: int, dist: str = "mixture", seed: int = 0,
-                 vocab: int = 32000, max_doc_len: int | None = None):
+                 vocab: int = 32000, max_doc_len: int | None = None, shape: dict | None = None):
+        """``shape``: up_sample_factor / filter_threshold / filter_ratio / elongate_factor / change_long_doc_ratio
+        for the ``wlbllm`` and ``prolong`` distributions (see :func:`sample_histogram`)."""
         self.tokens_per_seq, self.num_seqs, self.dist = tokens_per_seq, num_seqs, dist
         self.vocab = vocab
         self.max_doc_len = max_doc_len or tokens_per_seq
+        self.shape = dict(shape or {})
         self.rng = np.random.default_rng(seed)
 
     def next_doc_lens(self) -> list[list[int]]:
         packs: list[list[int]] = []
         while len(packs) < self.num_seqs:
             need = self.num_seqs - len(packs)
-            lens = sample_doc_lens(self.rng, max(8, 4 * need), self.dist, self.max_doc_len)
+            lens = sample_doc_lens(self.rng, max(8, 4 * need), self.dist, self.max_doc_len, **self.shape)
             packs += pack_documents(lens, self.tokens_per_seq, max_packs=need)
         return packs
 

@@ -43,10 +43,13 @@ def parse_args(argv=None):
     ap.add_argument("--pp-size", type=int, default=1)
     ap.add_argument("--num-microbatch", type=int, default=1)
     ap.add_argument("--use-planner", action="store_true", default=True)
-    ap.add_argument("--up-sample-factor", type=int, default=1)
+    # shaping of the wlbllm / prolong length distributions and of local corpora, with the reference's defaults
+    # (pretrain_llama.py:887-901): documents below the threshold are kept with probability filter-ratio, longer
+    # ones count up-sample-factor times, lengths are stretched by elongate-factor
+    ap.add_argument("--up-sample-factor", type=int, default=4)
     ap.add_argument("--elongate-factor", type=int, default=1)
-    ap.add_argument("--filter-threshold", type=int, default=0)
-    ap.add_argument("--filter-ratio", type=float, default=1.0)
+    ap.add_argument("--filter-threshold", type=int, default=65536)
+    ap.add_argument("--filter-ratio", type=float, default=0.50)
     ap.add_argument("--sample-name", default="mixture",
                     choices=["wlbllm", "prolong", "mixture", "loguniform", "loguniform64", "full",
                              "bookcorpus", "wikitext", "openwebtext", "c4"])
@@ -224,7 +227,10 @@ def main(argv=None) -> int:
                              a.elongate_factor, a.up_sample_factor, a.filter_threshold, a.filter_ratio)
     src = BatchSource(cfg, par, a.num_tokens, a.sample_name if a.sample_name in
                       ("wlbllm", "prolong", "mixture", "loguniform", "loguniform64", "full") else "wlbllm",
-                      seed=a.seed, seqs_per_rank=seqs_per_rank, stream=stream)
+                      seed=a.seed, seqs_per_rank=seqs_per_rank, stream=stream,
+                      shape=dict(up_sample_factor=a.up_sample_factor, filter_threshold=a.filter_threshold,
+                                 filter_ratio=a.filter_ratio, elongate_factor=a.elongate_factor,
+                                 change_long_doc_ratio=a.change_long_doc_ratio))
     src.stream.max_doc_len = min(max_len, a.num_tokens)
     log.info("model %s (%.2fB params) world %d = tp%d x pp%d x dp%d, cad=%s recompute=%s", cfg.name,
              cfg.num_params() / 1e9, world, par.tp, par.pp, par.dp, cad, recompute)
