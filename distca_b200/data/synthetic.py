@@ -115,17 +115,24 @@ class SyntheticBatches:
     """Endless stream of global batches: ``num_seqs`` packs of ``tokens_per_seq`` tokens each."""
 
     def __init__(self, tokens_per_seq: int, num_seqs: int, dist: str = "mixture", seed: int = 0,
-                 vocab: int = 32000, max_doc_len: int | None = None, shape: dict | None = None):
+                 vocab: int = 32000, max_doc_len: int | None = None, shape: dict | None = None,
+                 debug_packs: int = 0):
         """``shape``: up_sample_factor / filter_threshold / filter_ratio / elongate_factor / change_long_doc_ratio
-        for the ``wlbllm`` and ``prolong`` distributions (see :func:`sample_histogram`)."""
+        for the ``wlbllm`` and ``prolong`` distributions (see :func:`sample_histogram`). ``debug_packs``: the first
+        so many packs of the stream hold ONE document of the full length each (the reference's manual debug
+        cases, distca/utils/global_batch_provider.py:132-152: the heaviest, perfectly balanced workload)."""
         self.tokens_per_seq, self.num_seqs, self.dist = tokens_per_seq, num_seqs, dist
         self.vocab = vocab
         self.max_doc_len = max_doc_len or tokens_per_seq
         self.shape = dict(shape or {})
+        self.debug_packs = int(debug_packs)
         self.rng = np.random.default_rng(seed)
 
     def next_doc_lens(self) -> list[list[int]]:
         packs: list[list[int]] = []
+        while self.debug_packs > 0 and len(packs) < self.num_seqs:
+            packs.append([self.tokens_per_seq])
+            self.debug_packs -= 1
         while len(packs) < self.num_seqs:
             need = self.num_seqs - len(packs)
             lens = sample_doc_lens(self.rng, max(8, 4 * need), self.dist, self.max_doc_len, **self.shape)

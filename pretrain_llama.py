@@ -88,14 +88,15 @@ def parse_args(argv=None):
     ap.add_argument("--model-path", default=None, help="HuggingFace config.json (or its directory)")
     ap.add_argument("--num-layers", type=int, default=None)
     ap.add_argument("--max-sample-id", type=int, default=3, help="number of training steps")
-    ap.add_argument("--should-add-debug-cases", action="store_true")
+    ap.add_argument("--should-add-debug-cases", action="store_true",
+                    help="start the stream with packs of one full-length document each (heaviest balanced case)")
     ap.add_argument("--val-every-n-steps", type=int, default=0)
     ap.add_argument("--ckpt-every-n-steps", type=int, default=0)
     ap.add_argument("--output-dir", default=None)
     ap.add_argument("--enable-wandb", action="store_true")
     ap.add_argument("--wandb-project", default="distca_b200")
     ap.add_argument("--wandb-run-name", default=None)
-    ap.add_argument("--allow-all-ranks-loss", action="store_true")
+    ap.add_argument("--allow-all-ranks-loss", action="store_true", help="every rank logs its step lines")
     # --- switches the reference keeps in the environment or in test scripts ---
     ap.add_argument("--model", default="tiny-128", help="preset: tiny | tiny-128 | small-128 | llama3-8b | codellama-34b")
     ap.add_argument("--cad", dest="cad", action="store_true", default=True)
@@ -188,6 +189,8 @@ def main(argv=None) -> int:
                                              comm_buffer_gb=a.comm_buffer_gb, nano_batches=tc.extra["nano_batches"],
                                              microbatches_in_flight=min(a.num_microbatch, a.pp_size) if a.pp_size > 1 else 1),
                           cap)
+    if a.allow_all_ranks_loss or os.environ.get("ALLOW_ALL_RANKS_LOSS", "0") == "1":
+        os.environ["DISTCA_LOG_ALL_RANKS"] = "1"          # every rank prints its step lines, not only rank 0
     log = get_logger(rank=rank, out_dir=a.output_dir)
     if a.bind_cpus:
         from distca_b200.utils import affinity
@@ -230,7 +233,8 @@ def main(argv=None) -> int:
                       seed=a.seed, seqs_per_rank=seqs_per_rank, stream=stream,
                       shape=dict(up_sample_factor=a.up_sample_factor, filter_threshold=a.filter_threshold,
                                  filter_ratio=a.filter_ratio, elongate_factor=a.elongate_factor,
-                                 change_long_doc_ratio=a.change_long_doc_ratio))
+                                 change_long_doc_ratio=a.change_long_doc_ratio),
+                      debug_packs=1200 if a.should_add_debug_cases else 0)
     src.stream.max_doc_len = min(max_len, a.num_tokens)
     log.info("model %s (%.2fB params) world %d = tp%d x pp%d x dp%d, cad=%s recompute=%s", cfg.name,
              cfg.num_params() / 1e9, world, par.tp, par.pp, par.dp, cad, recompute)

@@ -67,3 +67,11 @@ def test_packing_fills_every_pack_and_carries_cut_documents_over():
     m = sample_mixture(np.random.default_rng(0), 20000, 131072)
     assert 0.17 < (m >= 32768).mean() < 0.23
     assert sample_doc_lens(np.random.default_rng(0), 10, "full", 512).tolist() == [512] * 10
+
+
+def test_debug_cases_open_the_stream_with_full_length_documents():
+    sb = SyntheticBatches(4096, 2, "wlbllm", seed=0, debug_packs=3)
+    assert sb.next_doc_lens() == [[4096], [4096]]
+    second = sb.next_doc_lens()
+    assert second[0] == [4096] and len(second[1]) >= 1 and sum(second[1]) == 4096
+    assert sb.debug_packs == 0
