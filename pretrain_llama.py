@@ -156,6 +156,8 @@ def main(argv=None) -> int:
     par = ParallelConfig(tp=a.tp_size, pp=a.pp_size, dp=dp)
     if par.world != world:
         raise SystemExit(f"world size {world} != tp {a.tp_size} x pp {a.pp_size} x dp {dp}")
+    if a.num_gpus_per_node is not None and a.num_nodes * a.num_gpus_per_node != world:
+        raise SystemExit(f"world size {world} != --num-nodes {a.num_nodes} x --num-gpus-per-node {a.num_gpus_per_node}")
     if a.pp_size > 1 and a.num_microbatch < a.pp_size:
         raise SystemExit("--num-microbatch must be at least --pp-size")
     cfg = get_model_config(a.model_path or a.model, a.num_layers)
