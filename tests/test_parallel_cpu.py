@@ -261,3 +261,34 @@ def test_pipeline_schedule_has_standard_1f1b_depth():
                     assert when_b[(p + 1, mb)] == t - 1 and when_f[(p + 1, mb)] == when_f[(p, mb)] + 1
             # bubble: each stage is busy in 2M of its 2(M + pp - 1) slots
             assert abs((1 - 2 * M / (2 * (M + pp - 1))) - (pp - 1) / (M + pp - 1)) < 1e-12
+
+
+def test_pipeline_nano_batch_bookkeeping():
+    """Ping-pong inside pipeline stages: every rank's documents of a micro-batch are cut at the document boundary
+    nearest to half the tokens (same rule on every rank for every rank's list), stage inputs are split and joined
+    by the nano-batches' sequence-parallel row counts, and slot tables are built per nano-batch."""
+    import torch
+    from distca_b200.models.config import ParallelConfig
+    from distca_b200.parallel.pipeline import PipelineTrainer
+    from distca_b200.runtime.trainer import nano_cut
+    assert nano_cut([300, 200, 100, 400, 24]) == 2 and nano_cut([1024]) in (0, 1) and nano_cut([]) == 0
+    assert nano_cut([100, 900]) == 1 and nano_cut([512, 512]) == 1
+    tr = object.__new__(PipelineTrainer)
+    tr.nano, tr.par, tr.dp_rank = 2, ParallelConfig(tp=2, pp=2, dp=2), 1
+    mbs = [[[512, 256, 256], [1024]], [[128] * 8, [768, 256]]]           # [micro-batch][dp rank]
+    first, second = tr._nano_docs(mbs)
+    assert first == [[[512], [1024]], [[128] * 4, [768]]] or first == [[[512], []], [[128] * 4, [768]]]
+    for mb in range(2):
+        for d in range(2):
+            assert first[mb][d] + second[mb][d] == mbs[mb][d]
+    # slot tables of one nano-batch: stage p runs micro-batch slot - p forward, dummies elsewhere
+    assert tr._slot_docs(first, "fwd", 0) == [first[0][0], first[0][1], [], []]
+    assert tr._slot_docs(second, "bwd", 0) == [[], [], second[0][0], second[0][1]]
+    x = torch.arange(24.0).view(12, 2)
+    a, b = PipelineTrainer._split_rows(x, [4, 8])
+    assert a.shape[0] == 4 and b.shape[0] == 8 and torch.equal(PipelineTrainer._join_rows([a, b]), x)
+    a, b = PipelineTrainer._split_rows(x, [0, 12])
+    assert a is None and torch.equal(PipelineTrainer._join_rows([a, b]), x)
+    assert PipelineTrainer._split_rows(None, [4, 8]) == [None, None]
+    tr.nano = 1
+    assert tr._nano_docs(mbs) == [mbs]
