@@ -8,7 +8,9 @@ import pytest
 from distca_b200.data.synthetic import (SyntheticBatches, pack_documents, sample_doc_lens, sample_histogram,
                                         sample_mixture)
 
-REF_DATA = os.path.join(os.environ.get("DISTCA_REFERENCE_ROOT", "/root/reference"), "distca", "simulator", "data")
+_REPO = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+REF_DATA = os.path.join(os.environ.get("DISTCA_REFERENCE_ROOT", os.path.join(_REPO, "baseline", "_ref")),
+                        "distca", "simulator", "data")
 
 
 def test_data_set_distributions_have_the_reference_quantiles():
