@@ -225,6 +225,87 @@ def time_model_from_sweep(source, base: str = "b200"):
     return tm
 
 
+class NetworkModel:
+    """Time of a collective as a function of the bytes one rank moves: per ``(operation, world size)`` a table
+    of measured ``(bytes, milliseconds)`` points, interpolated linearly; below the smallest point the time is that
+    point's (launch and signalling latency), above the largest it grows in proportion (bandwidth). World sizes
+    without a table use the nearest measured one. The reference keeps the same kind of tables for NCCL all-reduce
+    and all-gather on H100 (distca/timemodule/network.py:3-97); these are filled by
+    ``python -m distca_b200.utils.net_bench`` (:meth:`from_sweep`)."""
+
+    def __init__(self, tables: dict | None = None):
+        self.tables: dict = {}
+        for (op, world), pts in (tables or {}).items():
+            self.tables[(op, int(world))] = sorted((float(b), float(ms)) for b, ms in pts)
+
+    def ops(self) -> list:
+        return sorted({op for op, _ in self.tables})
+
+    def ms(self, op: str, world: int, nbytes: float) -> float:
+        if world <= 1 or nbytes <= 0:
+            return 0.0
+        worlds = [w for o, w in self.tables if o == op]
+        if not worlds:
+            raise KeyError(f"no table for {op!r}")
+        pts = self.tables[(op, min(worlds, key=lambda w: (abs(w - world), w)))]
+        if nbytes <= pts[0][0]:
+            return pts[0][1]
+        if nbytes >= pts[-1][0]:
+            return pts[-1][1] * nbytes / pts[-1][0]
+        for (b0, t0), (b1, t1) in zip(pts, pts[1:]):
+            if b0 <= nbytes <= b1:
+                return t0 + (t1 - t0) * (nbytes - b0) / (b1 - b0)
+        return pts[-1][1]
+
+    def gbytes_per_s(self, op: str, world: int, nbytes: float) -> float:
+        t = self.ms(op, world, nbytes)
+        return nbytes / t / 1e6 if t > 0 else 0.0
+
+    @staticmethod
+    def from_sweep(source) -> "NetworkModel":
+        """From the JSON lines of ``net_bench`` (``{"kernel": "net_sweep", "op", "world", "bytes_per_rank", "ms"}``)."""
+        import json
+        if isinstance(source, (str, bytes)) or hasattr(source, "__fspath__"):
+            with open(source) as f:
+                lines = list(f)
+        else:
+            lines = list(source)
+        tables: dict = {}
+        for ln in lines:
+            if not isinstance(ln, dict):
+                ln = ln.strip()
+                if not ln.startswith("{"):
+                    continue
+                try:
+                    ln = json.loads(ln)
+                except ValueError:
+                    continue
+            if ln.get("kernel") == "net_sweep" and ln.get("ms") is not None:
+                tables.setdefault((ln["op"], int(ln["world"])), []).append((ln["bytes_per_rank"], ln["ms"]))
+        if not tables:
+            raise ValueError("no net_sweep rows")
+        return NetworkModel(tables)
+
+
+def default_network_model(kind: str = "b200") -> NetworkModel:
+    """Measured on one 8 x B200 NVSwitch box (CUDA events, maximum over ranks, bytes = what one rank sends to other
+    GPUs): ``push`` is this repository's peer-store kernel together with its signal round trip (the dispatch
+    micro-benchmark), ``all_to_all`` the pack + NCCL ``all_to_all_single`` + unpack twin of the same traffic,
+    ``all_reduce`` NCCL at 1 GiB (725 GB/s bus bandwidth), ``peer_copy`` a plain copy into a peer's memory
+    (770 GB/s per direction)."""
+    if kind != "b200":
+        raise ValueError(kind)
+    MB = 1e6
+    return NetworkModel({
+        ("push", 2): [(23.9 * MB, 0.098), (297.1 * MB, 0.772)],
+        ("push", 8): [(24.5 * MB, 0.145), (1038.4 * MB, 1.937)],
+        ("all_to_all", 2): [(23.9 * MB, 0.236), (297.1 * MB, 2.535)],
+        ("all_to_all", 8): [(24.5 * MB, 0.528), (1038.4 * MB, 3.597)],
+        ("all_reduce", 8): [(2**30, 2.0 * (7 / 8) * 2**30 / 725e9 * 1e3)],
+        ("peer_copy", 2): [(2**30, 2**30 / 770e9 * 1e3)],
+    })
+
+
 def default_time_model(kind: str = "b200"):
     """Attention/linear cost tables. ``b200``: measured with this repository's kernels on one B200
     (whole causal document, 32 query / 8 KV heads of 128, forward); ``h100``: the reference's

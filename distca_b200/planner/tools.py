@@ -29,7 +29,7 @@ import numpy as np
 from ..data.synthetic import SyntheticBatches
 from ..data.wlb import balance_documents
 from ..models.config import get_model_config
-from . import Planner, PlannerConfig, chunk_flops, default_time_model
+from . import Planner, PlannerConfig, chunk_flops, default_network_model, default_time_model
 
 
 def _planner(model: str, world: int, tokens: int, tolerance: float, tp: int = 1) -> Planner:
@@ -95,7 +95,8 @@ STORE_LINK_EFFICIENCY = 0.70     # peer stores from many CTAs against the measur
 TILE_LOAD_GBS = 300.0            # per-tile remote TMA loads (p2p-tile): coarse; the measured TP > 1 steps imply 135-570 GB/s
 
 
-def _tp_comm_ms(cfg, tok: int, tp: int, layers: float, link_bytes_per_ms: float, recompute: str, transport: str) -> float:
+def _tp_comm_ms(cfg, tok: int, tp: int, layers: float, link_bytes_per_ms: float, recompute: str, transport: str,
+                network=None) -> float:
     """Time of a tensor-parallel rank's all-gathers that is NOT hidden behind GEMMs, per step. ``gather``: every
     shard pushed once, then a local GEMM (serial); ``tile``: the GEMM loads remote tiles itself and re-fetches a
     tile once per N tile that uses it; ``nccl``: library collectives, all-gathers and reduce-scatters serial. The
@@ -107,25 +108,35 @@ def _tp_comm_ms(cfg, tok: int, tp: int, layers: float, link_bytes_per_ms: float,
     passes_rs = 2 + (1 if recompute != "none" else 0) + 2
     if transport == "nccl":
         return (passes_ag + passes_rs) * shard / link_bytes_per_ms * layers
+    # one peer-store all-gather: measured (`net_bench`'s push_all_gather table, bytes = one rank's own shard) when the
+    # network model has it, else the link at the efficiency the dispatch kernel's stores reach
+    if network is not None and "push_all_gather" in network.ops():
+        push = lambda b: network.ms("push_all_gather", tp, b / (tp - 1))
+    else:
+        push = lambda b: b / (link_bytes_per_ms * STORE_LINK_EFFICIENCY)
     if transport == "gather":
-        return passes_ag * shard / (link_bytes_per_ms * STORE_LINK_EFFICIENCY) * layers
+        return passes_ag * push(shard) * layers
     # per-tile loads: operand bytes x N tiles of the consuming GEMM (QKV, FC1 forward and recompute; dact, dattn backward)
     nt = lambda n: max(1.0, n / tp / 256.0)
     fwd = nt(cfg.qkv_dim) + nt(2 * cfg.ffn)
     bwd = nt(cfg.ffn) + nt(cfg.q_dim)
     tiles = fwd * (2 if recompute != "none" else 1) + bwd
     gathers = 2                                                # n2, n1 for the weight gradients (pushed once)
-    return (tiles * shard / (TILE_LOAD_GBS * 1e6) + gathers * shard / (link_bytes_per_ms * STORE_LINK_EFFICIENCY)) * layers
+    return (tiles * shard / (TILE_LOAD_GBS * 1e6) + gathers * push(shard)) * layers
 
 
 def predict_step_ms(cfg, tm, packs: list[list[int]], tokens: int, tp: int, pp: int, dp: int, microbatches: int,
                     mode: str, recompute: str = "keep_attn", tp_transport: str = "gather",
-                    tolerance: float = 0.02) -> dict:
+                    tolerance: float = 0.02, network=None) -> dict:
     """Predicted milliseconds of one training step (forward, recompute, backward, optimizer) of the global batch
     ``packs`` (document lengths per packed sequence, ``len(packs)`` a multiple of ``dp``) under one layout.
     ``mode``: ``cad`` (core attention spread over the dp x pp servers by the planner), ``local`` (every rank attends
     to its own documents) or ``percp`` (per-document context parallelism over the dp ranks, all-gathered K/V; no
-    pipeline stages). Returns the parts as well."""
+    pipeline stages). ``network``: a :class:`~distca_b200.planner.NetworkModel` (default: the measured B200 tables)
+    for the peer-store all-gathers and, where it has a table, the NCCL all-gather of the baseline. Returns the
+    parts as well."""
+    if network is None:
+        network = default_network_model("b200")
     L = cfg.num_layers
     ref = get_model_config("llama3-8b")
     per_rank_seqs = len(packs) // dp
@@ -138,7 +149,7 @@ def predict_step_ms(cfg, tm, packs: list[list[int]], tokens: int, tp: int, pp: i
     lin = passes_lin * tm.linear_ms_per_token * scale_lin * tok_rank / tp * (L / pp)
     lm = LM_HEAD_MS_PER_TOKEN * tok_rank / tp * (cfg.vocab * cfg.hidden) / (ref.vocab * ref.hidden)
     opt = OPTIMIZER_MS_8B * (cfg.flops_per_token_linear() / ref.flops_per_token_linear()) / (tp * pp * dp)
-    tp_comm = _tp_comm_ms(cfg, tok_rank, tp, L / pp, link, recompute, tp_transport)
+    tp_comm = _tp_comm_ms(cfg, tok_rank, tp, L / pp, link, recompute, tp_transport, network)
     heads = ATTENTION_IN_STEP * cfg.heads_q / 32.0 / tp
     whole = lambda n: tm.attn_ms_for(n, n)
     disp = 0.0
@@ -153,7 +164,8 @@ def predict_step_ms(cfg, tm, packs: list[list[int]], tokens: int, tp: int, pp: i
             attn_fwd += max(whole(x) / dp, 2.0 * whole(min(c, 128)))   # at least two (partial) tiles of work per document
         kv_bytes = sum(docs) * 2 * cfg.kv_dim / tp * 2 * (dp - 1) / dp  # K and V of every other rank, bf16
         passes_kv = 1 + (1 if recompute != "none" else 0) + 1 + 1       # all-gather fwd, recompute, bwd; reduce-scatter dK/dV
-        disp = passes_kv * kv_bytes / link * L
+        one = network.ms("all_gather", dp, kv_bytes / max(dp - 1, 1)) if "all_gather" in network.ops() else kv_bytes / link
+        disp = passes_kv * one * L
         attn = passes_attn * attn_fwd * heads * L
         servers = dp
     elif mode == "cad" and dp * pp > 1:
@@ -183,7 +195,7 @@ def predict_step_ms(cfg, tm, packs: list[list[int]], tokens: int, tp: int, pp: i
 def search_layouts(model: str, gpus: int, tokens: int, dist: str, iterations: int = 10, tolerance: float = 0.02,
                    seed: int = 0, microbatches: int | None = None, seqs_per_step: int | None = None,
                    recompute: str = "keep_attn", tp_transport: str = "gather", comm_buffer_gb: float = 4.0,
-                   capacity_gb: float = 180.0, time_model=None) -> dict:
+                   capacity_gb: float = 180.0, time_model=None, network=None) -> dict:
     """Predicted milliseconds per training step of a fixed global batch of ``seqs_per_step`` packed sequences
     (default: one per GPU) under every (tp, pp, dp) layout of ``gpus`` GPUs, with local attention, with core-attention
     disaggregation and (layouts without pipeline stages) with the per-document CP baseline."""
@@ -205,7 +217,7 @@ def search_layouts(model: str, gpus: int, tokens: int, dist: str, iterations: in
             res = {}
             for mode in ("local", "cad") + (("percp",) if pp == 1 and dp > 1 else ()):
                 res[mode] = float(np.mean([predict_step_ms(cfg, tm, packs, tokens, tp, pp, dp, M, mode, recompute,
-                                                           tp_transport, tolerance)["step_ms"] for packs in batches]))
+                                                           tp_transport, tolerance, network)["step_ms"] for packs in batches]))
             row = {"tp": tp, "pp": pp, "dp": dp, "microbatches": M if pp > 1 else 1,
                    "step_ms_local_attention": round(res["local"], 1), "step_ms_cad": round(res["cad"], 1)}
             if "percp" in res:
@@ -248,16 +260,22 @@ def main() -> None:
                     help="layouts: how a tensor-parallel all-gather reaches its GEMM (gather = --tp-transport p2p)")
     ap.add_argument("--sweep-file", default=None,
                     help="layouts: `kernel_bench --kernel attn_sweep` output of the target machine for the attention table")
+    ap.add_argument("--net-file", default=None,
+                    help="layouts: `python -m distca_b200.utils.net_bench` output of the target machine for the collectives")
     a = ap.parse_args()
     if a.tool == "layouts":
-        tm = None
+        tm = net = None
         if a.sweep_file:
             from . import time_model_from_sweep
             tm = time_model_from_sweep(a.sweep_file)
+        if a.net_file:
+            from . import NetworkModel
+            net = NetworkModel.from_sweep(a.net_file)
         print(json.dumps(search_layouts(a.model, a.world, a.tokens, a.dist, a.iterations, a.tolerance,
                                         microbatches=a.microbatches, seqs_per_step=a.seqs_per_step,
                                         recompute=a.recompute, tp_transport=a.tp_transport,
-                                        comm_buffer_gb=a.comm_buffer_gb, capacity_gb=a.capacity_gb, time_model=tm)))
+                                        comm_buffer_gb=a.comm_buffer_gb, capacity_gb=a.capacity_gb, time_model=tm,
+                                        network=net)))
         return
     f = {"buffer": recommend_buffer_gb, "compare": compare_policies}[a.tool]
     print(json.dumps(f(a.model, a.world, a.tokens, a.dist, a.iterations, a.tolerance)))

@@ -53,3 +53,18 @@ def test_two_case_sweep_on_gloo_ranks(tmp_path):
     a, b = (x["result"]["last_loss"] for x in rows)
     assert abs(a - b) < 1e-4, (a, b)
     assert "tokens/s" in r.stdout and "percp" in r.stdout
+
+
+def test_collective_micro_benchmark_on_gloo_ranks_feeds_the_network_model():
+    from distca_b200.planner import NetworkModel
+    env = dict(os.environ, CUDA_VISIBLE_DEVICES="", OMP_NUM_THREADS="2")
+    cmd = [sys.executable, "-m", "torch.distributed.run", "--nnodes=1", "--nproc-per-node=2", "--master-addr", "127.0.0.1",
+           "--master-port", "29731", "-m", "distca_b200.utils.net_bench", "--sizes-mb", "1", "4", "--iters", "2", "--warmup", "1",
+           "--ops", "all_gather", "all_reduce", "all_to_all", "push_all_gather"]
+    r = subprocess.run(cmd, cwd=ROOT, env=env, capture_output=True, text=True, timeout=600)
+    assert r.returncode == 0, r.stdout[-2000:] + r.stderr[-2000:]
+    rows = [json.loads(l) for l in r.stdout.splitlines() if l.startswith("{")]
+    assert {x["op"] for x in rows} == {"all_gather", "all_reduce", "all_to_all"}      # the peer-store kernel needs GPUs
+    assert all(x["world"] == 2 and x["ms"] > 0 and x["bus_gbs"] > 0 for x in rows) and len(rows) == 6
+    net = NetworkModel.from_sweep(r.stdout.splitlines())
+    assert net.ms("all_gather", 2, rows[0]["bytes_per_rank"]) == rows[0]["ms"]

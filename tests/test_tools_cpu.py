@@ -279,3 +279,35 @@ def test_cpu_affinity_slices_are_disjoint_and_the_environment_record_is_written(
     path = affinity.dump_environment(str(tmp_path), rank=3, local_rank=1)
     text = open(path).read()
     assert path.endswith(".r3.lr1.env") and "PATH=" in text and "# cpus: " in text
+
+
+def test_network_model_interpolates_and_feeds_the_step_model(tmp_path):
+    """Collective time tables: latency floor below the smallest measured size, linear in between, bandwidth-
+    proportional above; world sizes without a table use the nearest one; a `net_bench` file replaces the built-in
+    estimate of the peer-store all-gather in the step model."""
+    import json
+    from distca_b200.models.config import get_model_config
+    from distca_b200.planner import NetworkModel, default_network_model, default_time_model
+    from distca_b200.planner.tools import predict_step_ms
+    from distca_b200.utils.net_bench import bus_bytes
+    n = NetworkModel({("all_gather", 8): [(1e6, 0.05), (1e8, 0.5), (1e9, 4.0)]})
+    assert n.ms("all_gather", 8, 1e3) == 0.05 and n.ms("all_gather", 8, 1e8) == 0.5
+    assert abs(n.ms("all_gather", 8, 5.5e8) - 2.25) < 1e-9 and abs(n.ms("all_gather", 8, 2e9) - 8.0) < 1e-9
+    assert n.ms("all_gather", 4, 1e8) == 0.5 and n.ms("all_gather", 1, 1e8) == 0.0
+    import pytest
+    with pytest.raises(KeyError):
+        n.ms("all_reduce", 8, 1e6)
+    d = default_network_model()
+    assert 500 < d.gbytes_per_s("push", 8, 1.0384e9) < 560 and d.ms("push", 8, 1e6) == 0.145
+    assert bus_bytes("all_reduce", 8, 2**30) == 2 * 2**30 * 7 / 8 and bus_bytes("all_gather", 8, 100) == 700
+    # a measured sweep: slow peer stores make the gather transport slower in the prediction
+    p = tmp_path / "net.jsonl"
+    rows = [{"kernel": "net_sweep", "op": "push_all_gather", "world": 2, "bytes_per_rank": b, "ms": b / 100e6}
+            for b in (16e6, 256e6, 1024e6)]                       # 100 GB/s
+    p.write_text("hello\n" + "\n".join(json.dumps(r) for r in rows) + "\n")
+    slow = NetworkModel.from_sweep(str(p))
+    cfg, tm = get_model_config("llama3-8b"), default_time_model("b200")
+    packs = [[131072]] * 4
+    a = predict_step_ms(cfg, tm, packs, 131072, 2, 1, 2, 1, "cad")
+    b = predict_step_ms(cfg, tm, packs, 131072, 2, 1, 2, 1, "cad", network=slow)
+    assert b["tp_comm_ms"] > 4 * a["tp_comm_ms"] and abs((b["step_ms"] - a["step_ms"]) - (b["tp_comm_ms"] - a["tp_comm_ms"])) < 1e-6
