@@ -75,10 +75,11 @@ def _args():
     ap.add_argument("--config", default="headline", choices=["headline", *NAMED_CONFIGS],
                     help="headline: the dp{N} + CAD scaling benchmark (default); the others are fixed 8-GPU layouts: "
                          + "; ".join(f"{k}: {v['what']}" for k, v in NAMED_CONFIGS.items()))
-    ap.add_argument("--baseline-mode", default="none", choices=["none", "percp"],
+    ap.add_argument("--baseline-mode", default="none", choices=["none", "percp", "perseq"],
                     help="percp: the no-CAD per-document context-parallel baseline on the same documents (all-gather K/V; "
                          "with --config: tensor parallel x context parallel over the remaining ranks; on the headline "
-                         "layout: context parallel over all GPUs)")
+                         "layout: context parallel over all GPUs); perseq: the same with packed sequences cut over the "
+                         "ranks instead of documents (per-sequence context parallelism)")
     ap.add_argument("--microbatches", type=int, default=None, help="micro-batches per step of a pipelined --config")
     ap.add_argument("--phase-timers", action="store_true",
                     help="CUDA-event phase timers in the device-timed region; the JSON line gains phases_ms_per_step")
@@ -179,7 +180,7 @@ def run_named_config(a) -> None:
     tp, pp, dp = spec["tp"], spec["pp"], spec["dp"]
     M = a.microbatches or spec["microbatches"]
     seq_len = a.seq_len or spec["seq_len"]
-    percp = a.baseline_mode == "percp"
+    percp = a.baseline_mode in ("percp", "perseq")       # perseq: chunks of packed sequences instead of documents
     seqs_per_step = dp * spec["seqs_per_rank"] * (M if pp > 1 else 1)
     if percp:
         # same global batch; pipeline and data-parallel ranks become one context-parallel group
@@ -190,7 +191,7 @@ def run_named_config(a) -> None:
     recompute = a.recompute or spec["recompute"]
     tc = TrainConfig(cad=not (a.no_cad or percp), recompute=recompute, comm_buffer_gb=a.comm_buffer_gb)
     tc.extra.update(tolerance=a.tolerance, attention_policy=a.attention_policy, fuse_qkv_rope=not a.no_fuse_qkv_rope,
-                    baseline_mode=a.baseline_mode)
+                    baseline_mode=a.baseline_mode, cp_seq_len=seq_len)
     if pp > 1 and tc.cad:
         tc.extra["nano_batches"] = a.nano_batches     # ping-pong nano-batches inside the pipeline stages
     if pp > 1:
@@ -270,7 +271,7 @@ def run_named_config(a) -> None:
             "higher_is_better": True, "scaling": "fixed 8-GPU layout", "vs_baseline": None, "dtype": "bf16",
             "data": f"synthetic packed documents ({spec['dist']}), random-init weights",
             "config": {"model": cfg.name, "layers": cfg.num_layers, "global_batch": seqs_per_step, "seq_len": seq_len,
-                       "parallelism": f"tp{tp}-" + (f"cp{dp}-percp" if percp else f"pp{pp}-dp{dp}" + ("-cad" if cad_rt is not None else "")),
+                       "parallelism": f"tp{tp}-" + (f"cp{dp}-{a.baseline_mode}" if percp else f"pp{pp}-dp{dp}" + ("-cad" if cad_rt is not None else "")),
                        "microbatches": M if pp > 1 else 1, "recompute": recompute,
                        "nano_batches": int(tc.extra.get("nano_batches", 1)),
                        "grad_dtype": str(trainer.model.store.grad.dtype).replace("torch.", ""),
@@ -314,7 +315,7 @@ def main() -> None:
     if a.config != "headline":
         run_named_config(a)
         return
-    if a.baseline_mode == "percp":
+    if a.baseline_mode in ("percp", "perseq"):
         # the headline layout (one 128K pack per GPU) under per-document context parallelism instead of CAD:
         # the like-for-like arm of the two attention schemes (same documents, same GPUs, TP = PP = 1)
         NAMED_CONFIGS["headline_layout"] = {

@@ -43,6 +43,36 @@ def percp_layout(doc_lens: list[int], world: int, rank: int) -> list[tuple[int, 
     return out
 
 
+def perseq_layout(doc_lens: list[int], world: int, rank: int, seq_len: int) -> list[tuple[int, int, int, int]]:
+    """Per-SEQUENCE context parallelism: the documents are taken as packed sequences of ``seq_len`` tokens
+    (consecutive documents that add up to ``seq_len``), every sequence is cut into ``2 * world`` equal chunks
+    wherever the document boundaries are, and rank ``rank`` owns chunk ``rank`` and chunk ``2 * world - 1 - rank``
+    of every sequence. Returns the segments ``(doc, a, b, row0)`` those chunks are made of. Tokens are balanced,
+    causal work is not: a chunk that holds the end of a long document carries far more than one that holds short
+    ones (the reference's second baseline, baseline/wlbllm_original/wlbllm/per_seq_cp_attn.py:26-57, 123-124)."""
+    assert seq_len % (2 * world) == 0, f"sequence of {seq_len} tokens is not a multiple of 2 x {world}"
+    c = seq_len // (2 * world)
+    out, row = [], 0
+    seq_docs, acc = [], 0          # (doc index, length) of the sequence being filled
+    for d, L in enumerate(doc_lens):
+        seq_docs.append((d, int(L)))
+        acc += int(L)
+        assert acc <= seq_len, "documents do not pack into sequences of seq_len tokens"
+        if acc < seq_len:
+            continue
+        for lo in (rank * c, (2 * world - 1 - rank) * c):          # head chunk, tail chunk in sequence coordinates
+            hi, start = lo + c, 0
+            for dd, LL in seq_docs:
+                a, b = max(lo, start) - start, min(hi, start + LL) - start
+                if b > a:
+                    out.append((dd, a, b, row))
+                    row += b - a
+                start += LL
+        seq_docs, acc = [], 0
+    assert not seq_docs, "the last sequence is incomplete"
+    return out
+
+
 def round_documents(doc_lens: list[int], world: int) -> list[int]:
     """Document lengths rounded so that each is a multiple of ``2 * world`` while the total is unchanged
     (tokens move between neighbouring documents); the total must itself be such a multiple."""
@@ -66,44 +96,49 @@ class PerDocCPAttention(TwoPhaseCoreAttention):
     """Core attention of one rank of a per-document context-parallel group (same interface as
     :class:`~distca_b200.models.llama.LocalCoreAttention`)."""
 
-    def __init__(self, cfg: ModelConfig, group, world: int, rank: int, device, tp: int = 1):
+    def __init__(self, cfg: ModelConfig, group, world: int, rank: int, device, tp: int = 1, seq_len: int | None = None):
+        """``seq_len``: cut packed sequences of that many tokens instead of documents (per-sequence CP,
+        :func:`perseq_layout`)."""
         self.hq, self.hkv, self.D = cfg.heads_q // tp, cfg.heads_kv // tp, cfg.head_dim
         self.group, self.W, self.me = group, world, rank
+        self.seq_len = seq_len
         self.device = torch.device(device)
         self.plan: attn_ops.AttnPlan | None = None
         self.scratch = attn_ops.BwdScratch()
         self.bytes_per_layer = 0       # K/V bytes this rank receives per layer forward (for reports)
 
     # ------------------------------------------------------------------------------------------
+    def layout(self, doc_lens: list[int], rank: int | None = None):
+        """Segments ``(doc, a, b, row0)`` of ``rank`` (default: this rank) for the global batch ``doc_lens``."""
+        r = self.me if rank is None else rank
+        if self.seq_len:
+            return perseq_layout(doc_lens, self.W, r, self.seq_len)
+        return percp_layout(doc_lens, self.W, r)
+
     def set_batch(self, doc_lens: list[int]) -> None:
         """``doc_lens``: every document of the GLOBAL batch, in order (all ranks pass the same list)."""
         W, me = self.W, self.me
         lens = np.asarray(doc_lens, dtype=np.int64)
-        c = lens // (2 * W)
-        T_local = int(2 * c.sum())
         total = int(lens.sum())
-        doc_row0_local = np.concatenate([[0], np.cumsum(2 * c)[:-1]])       # first local row of a document (any rank)
+        T_local = total // W
         doc_row0_global = np.concatenate([[0], np.cumsum(lens)[:-1]])       # first row in per-document order
         # gathered buffer row (rank-major: rank * T_local + local row) of every token in per-document order
         perm = np.empty(total, dtype=np.int64)
-        for d in range(len(lens)):
-            cd, g0, l0 = int(c[d]), int(doc_row0_global[d]), int(doc_row0_local[d])
-            for j in range(2 * W):
-                r = j if j < W else 2 * W - 1 - j
-                local = l0 + (0 if j < W else cd)
-                perm[g0 + j * cd:g0 + (j + 1) * cd] = r * T_local + local + np.arange(cd)
+        mine = None
+        for r in range(W):
+            segs = self.layout(doc_lens, r)
+            assert sum(b - a for _, a, b, _ in segs) == T_local, "ranks own unequal token counts"
+            for d, a, b, row0 in segs:
+                g0 = int(doc_row0_global[d])
+                perm[g0 + a:g0 + b] = r * T_local + row0 + np.arange(b - a)
+            if r == me:
+                mine = segs
         inv = np.empty(total, dtype=np.int64)
         inv[perm] = np.arange(total)
         self.perm = torch.from_numpy(perm).to(self.device)
         self.inv = torch.from_numpy(inv).to(self.device)
-        # this rank's tasks: head chunk sees keys [0, (me+1)c), tail chunk sees keys [0, (2W-me)c)
-        tasks = []
-        for d in range(len(lens)):
-            cd, g0, l0 = int(c[d]), int(doc_row0_global[d]), int(doc_row0_local[d])
-            if cd == 0:
-                continue
-            tasks.append((l0, cd, g0, (me + 1) * cd))
-            tasks.append((l0 + cd, cd, g0, (2 * W - me) * cd))
+        # this rank's tasks: the query rows of a segment see the keys of their document up to the segment's end
+        tasks = [(row0, b - a, int(doc_row0_global[d]), b) for d, a, b, row0 in mine if b > a]
         self.plan = attn_ops.AttnPlan(attn_ops.AttnTasks.from_lists(tasks), self.device)
         self.T_local, self.total = T_local, total
         self.bytes_per_layer = (W - 1) * T_local * 2 * self.hkv * self.D * 2

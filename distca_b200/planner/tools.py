@@ -131,8 +131,8 @@ def predict_step_ms(cfg, tm, packs: list[list[int]], tokens: int, tp: int, pp: i
     """Predicted milliseconds of one training step (forward, recompute, backward, optimizer) of the global batch
     ``packs`` (document lengths per packed sequence, ``len(packs)`` a multiple of ``dp``) under one layout.
     ``mode``: ``cad`` (core attention spread over the dp x pp servers by the planner), ``local`` (every rank attends
-    to its own documents) or ``percp`` (per-document context parallelism over the dp ranks, all-gathered K/V; no
-    pipeline stages). ``network``: a :class:`~distca_b200.planner.NetworkModel` (default: the measured B200 tables)
+    to its own documents) or ``percp`` / ``perseq`` (per-document / per-sequence context parallelism over the dp ranks,
+    all-gathered K/V; no pipeline stages). ``network``: a :class:`~distca_b200.planner.NetworkModel` (default: the measured B200 tables)
     for the peer-store all-gathers and, where it has a table, the NCCL all-gather of the baseline. Returns the
     parts as well."""
     if network is None:
@@ -153,7 +153,19 @@ def predict_step_ms(cfg, tm, packs: list[list[int]], tokens: int, tp: int, pp: i
     heads = ATTENTION_IN_STEP * cfg.heads_q / 32.0 / tp
     whole = lambda n: tm.attn_ms_for(n, n)
     disp = 0.0
-    if mode == "percp":
+    if mode == "perseq":
+        assert pp == 1, "the per-sequence CP baseline has no pipeline stages"
+        # every packed sequence cut into 2 x dp chunks wherever its documents end: tokens are balanced, causal work
+        # is not; the step waits for the rank whose chunks hold the ends of the long documents
+        from ..parallel.percp import perseq_layout
+        docs = [x for p_ in packs for x in p_]
+        per = [sum(tm.attn_ms_for(b - a, b) for _, a, b, _ in perseq_layout(docs, dp, r, tokens)) for r in range(dp)]
+        kv_bytes = sum(docs) * 2 * cfg.kv_dim / tp * 2 * (dp - 1) / dp
+        passes_kv = 1 + (1 if recompute != "none" else 0) + 1 + 1
+        one = network.ms("all_gather", dp, kv_bytes / max(dp - 1, 1)) if "all_gather" in network.ops() else kv_bytes / link
+        disp = passes_kv * one * L
+        attn = passes_attn * max(per) * heads * L
+    elif mode == "percp":
         assert pp == 1, "the per-document CP baseline has no pipeline stages"
         # every document cut into 2 x dp chunks, every rank holds a head and a tail chunk: 1 / dp of each document's
         # pairs, but 2 query chunks per document and rank (short documents pay the per-tile cost dp times over)
@@ -215,13 +227,14 @@ def search_layouts(model: str, gpus: int, tokens: int, dist: str, iterations: in
             if (seqs // dp) % M and pp > 1:
                 continue
             res = {}
-            for mode in ("local", "cad") + (("percp",) if pp == 1 and dp > 1 else ()):
+            for mode in ("local", "cad") + (("percp", "perseq") if pp == 1 and dp > 1 else ()):
                 res[mode] = float(np.mean([predict_step_ms(cfg, tm, packs, tokens, tp, pp, dp, M, mode, recompute,
                                                            tp_transport, tolerance, network)["step_ms"] for packs in batches]))
             row = {"tp": tp, "pp": pp, "dp": dp, "microbatches": M if pp > 1 else 1,
                    "step_ms_local_attention": round(res["local"], 1), "step_ms_cad": round(res["cad"], 1)}
             if "percp" in res:
                 row["step_ms_percp"] = round(res["percp"], 1)
+                row["step_ms_perseq"] = round(res["perseq"], 1)
             # per-GPU memory of the layout with disaggregation (tokens of one micro-batch per data-parallel rank)
             from ..models.config import ParallelConfig
             from ..utils.guards import estimate_memory_gb

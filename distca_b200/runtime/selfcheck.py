@@ -136,7 +136,8 @@ def check_percp(a) -> int:
     out = {}
     for mode in ("cad", "percp"):
         tc = TrainConfig(cad=(mode == "cad"), recompute=a.recompute, lr=1e-3)
-        tc.extra["baseline_mode"] = "percp" if mode == "percp" else "none"
+        tc.extra["baseline_mode"] = a.baseline if mode == "percp" else "none"
+        tc.extra["cp_seq_len"] = a.tokens
         tr = Trainer(cfg, par, tc, seed=1)
         src = BatchSource(cfg, par, a.tokens, a.dist, seed=a.seed)
         losses = []
@@ -253,6 +254,8 @@ def main() -> None:
     ap.add_argument("--pp", type=int, default=1)
     ap.add_argument("--microbatches", type=int, default=2)
     ap.add_argument("--nano", type=int, default=1, choices=[1, 2], help="ping-pong nano-batches in the CAD run")
+    ap.add_argument("--baseline", default="percp", choices=["percp", "perseq"],
+                    help="percp check: per-document or per-sequence context parallelism as the baseline arm")
     ap.add_argument("--fuse-ticks", action="store_true", help="with --nano 2: the next layer's pre-attention half per nano-batch right after this layer's post-attention half")
     ap.add_argument("--recompute", default="full", choices=["full", "keep_attn"],
                     help="activation policy of the CAD run (the local run always recomputes fully)")

@@ -205,11 +205,14 @@ class Trainer:
             self.core_attn = self.cad
         # baseline: per-document context parallelism over the same ranks, no disaggregation (all-gather K/V)
         self.percp = None
-        if train_cfg.extra.get("baseline_mode", "none") == "percp" and par.dp * par.pp > 1:
-            assert self.cad is None and par.pp == 1, "--baseline-mode percp replaces CAD and has no pipeline stages"
+        if train_cfg.extra.get("baseline_mode", "none") in ("percp", "perseq") and par.dp * par.pp > 1:
+            assert self.cad is None and par.pp == 1, "the context-parallel baselines replace CAD and have no pipeline stages"
             from ..parallel.percp import PerDocCPAttention
+            seq_len = None
+            if train_cfg.extra["baseline_mode"] == "perseq":       # per-sequence CP: chunks of packed sequences
+                seq_len = int(train_cfg.extra["cp_seq_len"])
             self.percp = PerDocCPAttention(model_cfg, self.groups.attn_group, len(self.groups.attn_ranks),
-                                           self.groups.attn_ranks.index(self.rank), self.device, par.tp)
+                                           self.groups.attn_ranks.index(self.rank), self.device, par.tp, seq_len=seq_len)
             self.core_attn = self.percp
         # ping-pong: a second core-attention module (own arena, own plan) for the second nano-batch
         self.nano = int(train_cfg.extra.get("nano_batches", 1))
@@ -351,12 +354,11 @@ class Trainer:
             self.model.tp.ensure_fused(hb.ids.numel() // self.par.tp)
         if isinstance(hb, SpanHostBatch) and self.percp is not None:
             # baseline: every rank holds a head and a tail chunk of every document of the global batch
-            from ..parallel.percp import percp_layout
             W = self.percp.W
             if self.par.tp > 1:
                 self.model.tp.ensure_fused(int(hb.tokens.numel()) // W // self.par.tp)
             with timers.phase("plan"):
-                ids, labels, pos = hb.materialise(percp_layout(hb.doc_lens, W, self.percp.me),
+                ids, labels, pos = hb.materialise(self.percp.layout(hb.doc_lens),
                                                   int(hb.tokens.numel()) // W, pinned=self.device.type == "cuda")
                 self.percp.set_batch(hb.doc_lens)
             batch = Batch(ids.to(self.device, non_blocking=True), labels.to(self.device, non_blocking=True),

@@ -11,7 +11,8 @@ A case is the reference's positional tuple (benchmarks/example-4d-parallel/run4d
     model  nodes  batch  microbatches  tokens  mode  dp  pp  tp  [comment]
 
 ``mode``: ``distca`` (core-attention disaggregation), ``baseline`` (per-document context parallelism with
-all-gathered K/V, no disaggregation), ``local`` (every rank attends to its own documents), ``wlbllm`` (the
+all-gathered K/V, no disaggregation), ``perseq`` (per-sequence context parallelism: packed sequences cut over the
+ranks wherever their documents end), ``local`` (every rank attends to its own documents), ``wlbllm`` (the
 reference's third arm; here the same per-document CP attention, and its packing is compared offline by
 ``python -m distca_b200.planner.tools compare``). ``--cases-file`` reads one case per line (``#`` comments).
 A distribution is ``name change_long_doc_ratio``. ``nodes`` > 1 needs ``--nodes host1,host2,...`` (ssh, see
@@ -34,7 +35,7 @@ from dataclasses import asdict, dataclass
 
 from . import launch
 
-MODES = ("distca", "baseline", "local", "wlbllm")
+MODES = ("distca", "baseline", "perseq", "local", "wlbllm")
 ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
 
 
@@ -79,7 +80,7 @@ def script_args(c: Case, dist: str, ratio: float, out_dir: str, steps: int, gpus
     documents of the sampled data sets are stretched by ``tokens / 65536``, run4d.sh:118-121)."""
     if c.world != c.nodes * gpus_per_node:
         raise ValueError(f"{c}: dp*pp*tp = {c.world} but nodes*gpus = {c.nodes * gpus_per_node}")
-    if c.mode in ("baseline", "wlbllm") and c.pp > 1:
+    if c.mode in ("baseline", "perseq", "wlbllm") and c.pp > 1:
         raise ValueError(f"{c}: the per-document CP baseline runs without pipeline stages (use dp x tp)")
     a = [os.path.join(ROOT, "pretrain_llama.py"), "--model", c.model, "--num-nodes", str(c.nodes),
          "--num-gpus-per-node", str(gpus_per_node), "--tp-size", str(c.tp), "--pp-size", str(c.pp),
@@ -90,6 +91,8 @@ def script_args(c: Case, dist: str, ratio: float, out_dir: str, steps: int, gpus
         a.append("--cad")
     elif c.mode == "local":
         a.append("--no-cad")
+    elif c.mode == "perseq":
+        a += ["--baseline-mode", "perseq"]
     else:
         a += ["--baseline-mode", "percp"]
     return a + list(extra)

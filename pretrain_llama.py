@@ -104,10 +104,12 @@ def parse_args(argv=None):
     ap.add_argument("--comm-buffer-gb", type=float, default=float(os.environ.get("EXPERIMENT_NVSHMEM_BUFFER_SIZE_GB", 2.0)))
     ap.add_argument("--recompute", default=None, choices=["none", "selective", "full", "keep_attn"],
                     help="keep_attn (default without pipeline stages; with them: full): recompute every layer in backward except core attention, whose output is kept in HBM or pinned host memory; full: recompute whole layers; none: keep all activations")
-    ap.add_argument("--baseline-mode", default="none", choices=["none", "percp"],
+    ap.add_argument("--baseline-mode", default="none", choices=["none", "percp", "perseq"],
                     help="percp: no core-attention disaggregation; the data-parallel ranks form a per-document "
                          "context-parallel group instead (every document cut over all of them, K/V all-gathered, "
-                         "dK/dV reduce-scattered with NCCL): the comparison point of the reference's --mode wlbllm")
+                         "dK/dV reduce-scattered with NCCL): the comparison point of the reference's --mode wlbllm; "
+                         "perseq: the same with every packed SEQUENCE cut over the ranks wherever its documents end "
+                         "(per-sequence context parallelism: balanced tokens, unbalanced attention work)")
     ap.add_argument("--tp-transport", default="p2p", choices=["p2p", "p2p-tile", "nccl"],
                     help="tensor-parallel collectives: p2p = shards gathered once by peer stores + reduce-scatter in the "
                          "GEMM epilogue; p2p-tile = all-gather in the GEMM's operand load as well (every CTA loads the "
@@ -171,6 +173,7 @@ def main(argv=None) -> int:
     tc.extra["tolerance"] = a.tolerance
     tc.extra["attention_policy"] = a.attention_policy
     tc.extra["baseline_mode"] = a.baseline_mode
+    tc.extra["cp_seq_len"] = a.num_tokens          # per-sequence CP cuts every packed sequence over the ranks
     tc.extra["tp_transport"] = a.tp_transport
     tc.extra["dp_transport"] = a.dp_transport
     if a.wait_report_ms is not None:
@@ -179,8 +182,8 @@ def main(argv=None) -> int:
     tc.extra["fuse_ticks"] = a.fuse_ticks
     if a.cost_model_file:
         tc.extra["cost_model_file"] = a.cost_model_file
-    if a.baseline_mode == "percp" and a.pp_size > 1:
-        raise SystemExit("--baseline-mode percp has no pipeline stages: use --pp-size 1")
+    if a.baseline_mode in ("percp", "perseq") and a.pp_size > 1:
+        raise SystemExit(f"--baseline-mode {a.baseline_mode} has no pipeline stages: use --pp-size 1")
     # ping-pong nano-batches: in the non-pipelined trainer and inside pipeline stages alike
     tc.extra["nano_batches"] = 2 if (a.pingpong and cad and dp * a.pp_size > 1 and not a.span_documents) else 1
     if a.quit_if_maybe_oom:
@@ -248,7 +251,7 @@ def main(argv=None) -> int:
     from distca_b200.utils.guards import TrainingGuards
     from distca_b200.utils.profiler import ProfilerCtx
     guards = TrainingGuards(a.check_nan, a.check_for_spiky_loss, a.check_for_large_grads)
-    percp = a.baseline_mode == "percp" and par.dp > 1
+    percp = a.baseline_mode in ("percp", "perseq") and par.dp > 1
     draw = (lambda: src.next_global()) if percp else (lambda: src.next(trainer.dp_rank))
     for _ in range(start_it):
         draw()                        # resume: the data stream continues where the saved run stopped

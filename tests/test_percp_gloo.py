@@ -11,7 +11,7 @@ import torch.distributed as dist
 import torch.multiprocessing as mp
 
 from distca_b200.models.config import PRESETS, ParallelConfig, TrainConfig
-from distca_b200.parallel.percp import percp_layout, round_documents
+from distca_b200.parallel.percp import percp_layout, perseq_layout, round_documents
 
 
 def _free_port():
@@ -42,7 +42,26 @@ def test_layout_covers_every_token_once_and_balances_causal_work():
     assert round_documents([100, 30, 158], 4) == [96, 32, 160]
 
 
-def _worker(rank, world, port, q):
+def test_per_sequence_layout_balances_tokens_but_not_work():
+    docs, W, S = [200, 56, 256, 128, 128], 2, 256              # three packed sequences of 256 tokens
+    seen, work = {}, []
+    for r in range(W):
+        rows, pairs = 0, 0
+        for d, a, b, row0 in perseq_layout(docs, W, r, S):
+            assert row0 == rows and 0 <= a < b <= docs[d]
+            rows += b - a
+            for t in range(a, b):
+                assert (d, t) not in seen
+                seen[(d, t)] = r
+                pairs += t + 1
+        assert rows == sum(docs) // W
+        work.append(pairs)
+    assert len(seen) == sum(docs) and max(work) > min(work)      # document boundaries fall inside chunks
+    # a sequence that is one document: the same chunks as per-document CP
+    assert perseq_layout([256], 2, 1, 256) == percp_layout([256], 2, 1)
+
+
+def _worker(rank, world, port, q, mode="percp"):
     try:
         os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port), RANK=str(rank), WORLD_SIZE=str(world),
                           LOCAL_RANK=str(rank))
@@ -58,7 +77,8 @@ def _worker(rank, world, port, q):
         out = {}
         for rc in ("full", "keep_attn"):
             tc = TrainConfig(cad=False, recompute=rc, lm_head_chunk=2048, lr=0.0)
-            tc.extra["baseline_mode"] = "percp"
+            tc.extra["baseline_mode"] = mode
+            tc.extra["cp_seq_len"] = sum(docs)            # per-sequence CP: the whole batch is one packed sequence
             tr = Trainer(cfg, par, tc, device="cpu", seed=0)
             loss = tr.train_step(hb)
             g = tr.model.store.grad.clone()
@@ -86,12 +106,12 @@ def _worker(rank, world, port, q):
         q.put((rank, False, repr(e) + traceback.format_exc()))
 
 
-@pytest.mark.parametrize("world", [2, 4])
-def test_per_document_cp_matches_single_process(world):
+@pytest.mark.parametrize("world,mode", [(2, "percp"), (4, "percp"), (2, "perseq")])
+def test_per_document_cp_matches_single_process(world, mode):
     ctx = mp.get_context("spawn")
     q = ctx.Queue()
     port = _free_port()
-    procs = [ctx.Process(target=_worker, args=(r, world, port, q)) for r in range(world)]
+    procs = [ctx.Process(target=_worker, args=(r, world, port, q, mode)) for r in range(world)]
     for p in procs:
         p.start()
     results = [q.get(timeout=600) for _ in range(world)]
