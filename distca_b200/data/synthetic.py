@@ -116,7 +116,7 @@ class SyntheticBatches:
 
     def __init__(self, tokens_per_seq: int, num_seqs: int, dist: str = "mixture", seed: int = 0,
                  vocab: int = 32000, max_doc_len: int | None = None, shape: dict | None = None,
-                 debug_packs: int = 0):
+                 debug_packs: int = 0, packing: str = "sequential"):
         """``shape``: up_sample_factor / filter_threshold / filter_ratio / elongate_factor / change_long_doc_ratio
         for the ``wlbllm`` and ``prolong`` distributions (see :func:`sample_histogram`). ``debug_packs``: the first
         so many packs of the stream hold ONE document of the full length each (the reference's manual debug
@@ -126,6 +126,8 @@ class SyntheticBatches:
         self.max_doc_len = max_doc_len or tokens_per_seq
         self.shape = dict(shape or {})
         self.debug_packs = int(debug_packs)
+        assert packing in ("sequential", "wlb")
+        self.packing = packing          # wlb: workload-balanced packing of every global batch (data/wlb.py::pack_balanced)
         self.rng = np.random.default_rng(seed)
 
     def next_doc_lens(self) -> list[list[int]]:
@@ -133,6 +135,13 @@ class SyntheticBatches:
         while self.debug_packs > 0 and len(packs) < self.num_seqs:
             packs.append([self.tokens_per_seq])
             self.debug_packs -= 1
+        if self.packing == "wlb" and len(packs) < self.num_seqs:
+            from .wlb import pack_balanced
+            need, lens = self.num_seqs - len(packs), []
+            while sum(lens) < need * self.tokens_per_seq:
+                lens += [int(-(-x // 16) * 16) for x in
+                         sample_doc_lens(self.rng, max(8, 4 * need), self.dist, self.max_doc_len, **self.shape)]
+            return packs + pack_balanced(lens, need, self.tokens_per_seq)
         while len(packs) < self.num_seqs:
             need = self.num_seqs - len(packs)
             lens = sample_doc_lens(self.rng, max(8, 4 * need), self.dist, self.max_doc_len, **self.shape)

@@ -472,12 +472,12 @@ class BatchSource:
 
     def __init__(self, model_cfg: ModelConfig, par: ParallelConfig, tokens_per_seq: int, dist_name: str,
                  seed: int, seqs_per_rank: int = 1, pinned: bool = True, stream=None, shape: dict | None = None,
-                 debug_packs: int = 0):
+                 debug_packs: int = 0, packing: str = "sequential"):
         """``stream``: any object with ``next_doc_lens()`` / ``next_tokens(packs)`` (e.g.
         :class:`~distca_b200.data.text.TextBatches`); default: synthetic documents of ``dist_name``."""
         self.par = par
         self.stream = stream or SyntheticBatches(tokens_per_seq, par.dp * seqs_per_rank, dist_name, seed, model_cfg.vocab,
-                                                 shape=shape, debug_packs=debug_packs)
+                                                 shape=shape, debug_packs=debug_packs, packing=packing)
         self.seqs_per_rank = seqs_per_rank
         self.pinned = pinned and torch.cuda.is_available()
 

@@ -13,8 +13,7 @@ A case is the reference's positional tuple (benchmarks/example-4d-parallel/run4d
 ``mode``: ``distca`` (core-attention disaggregation), ``baseline`` (per-document context parallelism with
 all-gathered K/V, no disaggregation), ``perseq`` (per-sequence context parallelism: packed sequences cut over the
 ranks wherever their documents end), ``local`` (every rank attends to its own documents), ``wlbllm`` (the
-reference's third arm; here the same per-document CP attention, and its packing is compared offline by
-``python -m distca_b200.planner.tools compare``). ``--cases-file`` reads one case per line (``#`` comments).
+reference's third arm: per-document CP attention over workload-balanced packs, ``--packing wlb``). ``--cases-file`` reads one case per line (``#`` comments).
 A distribution is ``name change_long_doc_ratio``. ``nodes`` > 1 needs ``--nodes host1,host2,...`` (ssh, see
 :mod:`distca_b200.launch`). ``--dry-run`` (or ``DRY_RUN=1``) prints the commands only.
 
@@ -93,6 +92,8 @@ def script_args(c: Case, dist: str, ratio: float, out_dir: str, steps: int, gpus
         a.append("--no-cad")
     elif c.mode == "perseq":
         a += ["--baseline-mode", "perseq"]
+    elif c.mode == "wlbllm":
+        a += ["--baseline-mode", "percp", "--packing", "wlb"]
     else:
         a += ["--baseline-mode", "percp"]
     return a + list(extra)

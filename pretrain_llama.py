@@ -84,6 +84,9 @@ def parse_args(argv=None):
     ap.add_argument("--data-path", default=None, help="local .txt / .jsonl corpus instead of synthetic documents")
     ap.add_argument("--tokenizer-path", default=None, help="local Hugging Face tokenizer directory (default: UTF-8 bytes)")
     ap.add_argument("--change-long-doc-ratio", type=float, default=0.0)
+    ap.add_argument("--packing", default="sequential", choices=["sequential", "wlb"],
+                    help="wlb: workload-balanced packing of every global batch (WLB-LLM: documents longest first to the "
+                         "pack with the least (l/B)^2 + l/B work, equal tokens per pack) instead of packing in order")
     ap.add_argument("--max-total-tokens", type=int, default=None)
     ap.add_argument("--model-path", default=None, help="HuggingFace config.json (or its directory)")
     ap.add_argument("--num-layers", type=int, default=None)
@@ -239,7 +242,7 @@ def main(argv=None) -> int:
                       shape=dict(up_sample_factor=a.up_sample_factor, filter_threshold=a.filter_threshold,
                                  filter_ratio=a.filter_ratio, elongate_factor=a.elongate_factor,
                                  change_long_doc_ratio=a.change_long_doc_ratio),
-                      debug_packs=1200 if a.should_add_debug_cases else 0)
+                      debug_packs=1200 if a.should_add_debug_cases else 0, packing=a.packing)
     src.stream.max_doc_len = min(max_len, a.num_tokens)
     log.info("model %s (%.2fB params) world %d = tp%d x pp%d x dp%d, cad=%s recompute=%s", cfg.name,
              cfg.num_params() / 1e9, world, par.tp, par.pp, par.dp, cad, recompute)

@@ -77,3 +77,22 @@ def test_debug_cases_open_the_stream_with_full_length_documents():
     second = sb.next_doc_lens()
     assert second[0] == [4096] and len(second[1]) >= 1 and sum(second[1]) == 4096
     assert sb.debug_packs == 0
+
+
+def test_workload_balanced_packing_fills_equal_packs_and_evens_out_the_work():
+    from distca_b200.data.wlb import pack_balanced, workload
+    rng = np.random.default_rng(4)
+    T, n = 32768, 8
+    lens = []
+    while sum(lens) < n * T:
+        lens += [int(-(-x // 16) * 16) for x in sample_doc_lens(rng, 16, "loguniform", T // 2)]
+    bal = pack_balanced(lens, n, T, breakpoint=T)
+    seq = pack_documents(lens, T, max_packs=n)
+    assert len(bal) == n and all(sum(p) == T for p in bal) and all(x % 16 == 0 for p in bal for x in p)
+    spread = lambda packs: max(workload(p, T) for p in packs) / (sum(workload(p, T) for p in packs) / len(packs))
+    assert spread(bal) < spread(seq) and spread(bal) < 1.25
+    sb = SyntheticBatches(T, n, "mixture", seed=1, packing="wlb")
+    docs = sb.next_doc_lens()
+    assert len(docs) == n and all(sum(d) == T for d in docs)
+    ids, labels, pos = sb.next_tokens(docs)
+    assert ids.shape == (n, T) and int(pos.max()) < T
