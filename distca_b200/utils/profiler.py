@@ -71,3 +71,27 @@ class TraceFunctions:
     def __exit__(self, *exc):
         sys.settrace(None)
         return False
+
+
+def install_rank_excepthook(rank: int | None = None, out=None) -> None:
+    """Uncaught exceptions print as ``path:line: in function`` lines (clickable in editors and CI logs) followed by
+    the error with the rank in front, so that in the interleaved output of many ranks it is clear who failed
+    where. Reference: distca/utils/traceback.py:15-33 (``EXPERIMENT_PYTHON_BETTER_TRACEBACK``)."""
+    import traceback
+
+    def hook(exc_type, exc, tb):
+        f = out or sys.stderr
+        r = rank
+        if r is None:
+            try:
+                import torch.distributed as dist
+                r = dist.get_rank() if dist.is_initialized() else int(os.environ.get("RANK", "0"))
+            except Exception:
+                r = int(os.environ.get("RANK", "0"))
+        for fr in traceback.extract_tb(tb):
+            f.write(f"{os.path.abspath(fr.filename)}:{fr.lineno}: in {fr.name}\n")
+            if fr.line:
+                f.write(f"    {fr.line}\n")
+        f.write(f"[rank {r}] {exc_type.__name__}: {exc}\n")
+        f.flush()
+    sys.excepthook = hook

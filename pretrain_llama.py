@@ -157,6 +157,9 @@ def main(argv=None) -> int:
     from distca_b200.utils.observability import MemoryLog, RunArtifacts, get_logger, inspect_plan, nvtx_range
 
     rank, world, local = init_distributed()
+    if os.environ.get("EXPERIMENT_PYTHON_BETTER_TRACEBACK", "1") == "1":
+        from distca_b200.utils.profiler import install_rank_excepthook
+        install_rank_excepthook(rank)
     dp = a.dp_size or a.cp_size or max(1, world // (a.tp_size * a.pp_size))
     par = ParallelConfig(tp=a.tp_size, pp=a.pp_size, dp=dp)
     if par.world != world:

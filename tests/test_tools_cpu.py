@@ -311,3 +311,24 @@ def test_network_model_interpolates_and_feeds_the_step_model(tmp_path):
     a = predict_step_ms(cfg, tm, packs, 131072, 2, 1, 2, 1, "cad")
     b = predict_step_ms(cfg, tm, packs, 131072, 2, 1, 2, 1, "cad", network=slow)
     assert b["tp_comm_ms"] > 4 * a["tp_comm_ms"] and abs((b["step_ms"] - a["step_ms"]) - (b["tp_comm_ms"] - a["tp_comm_ms"])) < 1e-6
+
+
+def test_rank_excepthook_prints_clickable_frames_and_the_rank():
+    import io
+    import sys
+    from distca_b200.utils.profiler import install_rank_excepthook
+    old = sys.excepthook
+    buf = io.StringIO()
+    try:
+        install_rank_excepthook(5, out=buf)
+
+        def boom():
+            raise ValueError("plan does not fit")
+        try:
+            boom()
+        except ValueError:
+            sys.excepthook(*sys.exc_info())
+    finally:
+        sys.excepthook = old
+    text = buf.getvalue()
+    assert "[rank 5] ValueError: plan does not fit" in text and ": in boom" in text and __file__.split("/")[-1] in text
