@@ -73,14 +73,20 @@ def estimate_memory_gb(cfg: ModelConfig, par: ParallelConfig, tokens_per_rank: i
         q_b, kv_b = cfg.q_dim // par.tp * 2, cfg.kv_dim // par.tp * 2
         arena = (2 * T * q_b * 2 + max(comm_buffer_gb * 2**30 - 2 * T * q_b, 4 * T * kv_b) + T * q_b + T * qkvd * 2
                  + W * T * 2 * kv_b + 2 * T * (cfg.heads_q // par.tp) * 8) * nano_batches
-    total = weights + grads + optim + inputs + transient + head + arena
+    # peer arena of the tensor-parallel transports: one staging shard, tp reduce-scatter slots, tp gather slots
+    tp_arena = rows_sp * cfg.hidden * 2 * (1 + 2 * par.tp) if par.tp > 1 else 0.0
+    total = weights + grads + optim + inputs + transient + head + arena + tp_arena
+    # keep_attn: the kept attention outputs go to whatever HBM is left and then to host memory, so they never make a
+    # configuration fail; reported for information
+    kept = layers * microbatches_in_flight * T * (cfg.q_dim // par.tp + 2 * cfg.heads_q // par.tp) * 2 if recompute == "keep_attn" else 0.0
     return {"weights": weights / GB, "gradients": grads / GB, "optimizer": optim / GB, "layer_inputs": inputs / GB,
-            "transient": transient / GB, "lm_head": head / GB, "attention_arena": arena / GB, "total": total / GB}
+            "transient": transient / GB, "lm_head": head / GB, "attention_arena": arena / GB,
+            "tensor_parallel_arena": tp_arena / GB, "total": total / GB, "kept_attention_if_room": kept / GB}
 
 
 def quit_if_maybe_oom(est: dict, capacity_gb: float, margin: float = 0.97) -> None:
     if est["total"] > capacity_gb * margin:
-        parts = ", ".join(f"{k} {v:.1f}" for k, v in est.items() if k != "total")
+        parts = ", ".join(f"{k} {v:.1f}" for k, v in est.items() if k not in ("total", "kept_attention_if_room"))
         raise TrainingFault(f"estimated {est['total']:.1f} GB per GPU exceeds {capacity_gb:.0f} GB ({parts})")
 
 
