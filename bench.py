@@ -186,7 +186,8 @@ def run_named_config(a) -> None:
         # same global batch; pipeline and data-parallel ranks become one context-parallel group
         dp, pp = dp * pp, 1
     assert world == tp * pp * dp, f"--config {a.config} needs {tp * pp * dp} GPUs, WORLD_SIZE={world}"
-    cfg = get_model_config(spec["model"], a.num_layers)
+    # --model other than the default replaces the layout's model (debugging a layout on a small model)
+    cfg = get_model_config(spec["model"] if a.model == "llama3-8b" else a.model, a.num_layers)
     par = ParallelConfig(tp=tp, pp=pp, dp=dp)
     recompute = a.recompute or spec["recompute"]
     tc = TrainConfig(cad=not (a.no_cad or percp), recompute=recompute, comm_buffer_gb=a.comm_buffer_gb)

@@ -92,6 +92,9 @@ PRESETS: dict[str, ModelConfig] = {
     # Qwen2-shaped small model (QKV bias), the reference's second supported architecture
     "qwen2-tiny": ModelConfig(name="qwen2-tiny", num_layers=2, hidden=256, heads_q=4, heads_kv=2, head_dim=64,
                               ffn=688, vocab=32000, rope_theta=1000000.0, qkv_bias=True),
+    # the head layout of the large models in small (8 KV heads: divisible by every tensor-parallel size of one box)
+    "tiny-8kv": ModelConfig(name="tiny-8kv", num_layers=2, hidden=512, heads_q=16, heads_kv=8, head_dim=64,
+                            ffn=1024, vocab=4096, rope_theta=500000.0),
     "llama3-8b": ModelConfig(name="llama3-8b", num_layers=32, hidden=4096, heads_q=32, heads_kv=8, head_dim=128,
                              ffn=14336, vocab=128256, rope_theta=500000.0, max_position=131072),
     "codellama-34b": ModelConfig(name="codellama-34b", num_layers=48, hidden=8192, heads_q=64, heads_kv=8,
