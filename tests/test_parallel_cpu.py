@@ -40,10 +40,15 @@ class _GlooPeerCollectives:
         self.gathers += 1
         parts = [torch.empty_like(x) for _ in range(self.size)]
         dist.all_gather(parts, x.contiguous(), group=self.group)
-        return torch.cat(parts)
+        self._view = torch.cat(parts)
+        return self._view
 
     def release_gather(self):
+        """After the release the peers may overwrite the gather buffer: poison what was handed out, so that any
+        later read of it (a kernel queued after the release) turns the step's results into NaN."""
         self.releases += 1
+        self._view.fill_(float("nan"))
+        self._view = None
 
     def linear_rs(self, x, w, residual=None, transposed_weight=False):
         self.rs_calls += 1
