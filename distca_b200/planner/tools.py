@@ -61,7 +61,7 @@ def compare_policies(model: str, world: int, tokens: int, dist: str, iterations:
     p = _planner(model, world, tokens, tolerance)
     tm = default_time_model("b200")
     src = SyntheticBatches(tokens, world, dist, seed)
-    out = {"cad": [], "per_document_cp": [], "local": [], "wlb_packing": []}
+    out = {"cad": [], "per_document_cp": [], "per_sequence_cp": [], "local": [], "wlb_packing": []}
     traffic = {"cad": [], "per_document_cp": []}
     for _ in range(iterations):
         docs = src.next_doc_lens()
@@ -71,6 +71,10 @@ def compare_policies(model: str, world: int, tokens: int, dist: str, iterations:
             traffic[name].append(sum(float(np.asarray(plan.rank(r).send_bytes).sum() - plan.rank(r).send_bytes[r])
                                      for r in range(world)) / world / 1e6)
         whole = lambda L: tm.attn_ms_for(L, L)
+        from ..parallel.percp import perseq_layout
+        flat = [L for d in docs for L in d]
+        out["per_sequence_cp"].append(max(sum(tm.attn_ms_for(b - a, b) for _, a, b, _ in perseq_layout(flat, world, r, tokens))
+                                          for r in range(world)))
         out["local"].append(max(sum(whole(L) for L in d) for d in docs))
         bins = balance_documents([L for d in docs for L in d], world, 2 * tokens)
         out["wlb_packing"].append(max(sum(whole(L) for L in b) for b in bins))
